@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define LIA_ABI_VERSION 5
+#define LIA_ABI_VERSION 6
 
 typedef void* lia_stream_t; /* cudaStream_t */
 
@@ -253,6 +253,51 @@ int lia_program_run(LiaProgram* p, int pos0, const int64_t* ids_in, int64_t* ids
 int lia_program_error(LiaProgram* p);                           /* 0 = ok, 1 = a CTA timed out; synchronises the device */
 int lia_program_num_ops(LiaProgram* p);
 int lia_program_destroy(LiaProgram* p);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Models with a 32-bit residual stream, recurrent (matrix-memory) mixers and latent-cache attention.
+ * Flags `*_f32` say whether a buffer holds fp32 (1) or bf16 (0); norm weights, biases, gates, state and the residual
+ * stream are always fp32.  `segs[s] = {slot, first position, first row, rows}` describes the portion of sequence `slot`
+ * that occupies rows [first row, first row + rows) of the step; `meta[row] = {slot, position}` says the same per row.
+ * The reference has none of these (its only model family is OPT). */
+
+/* x[row] = w * e / sqrt(mean(e^2) + eps), e = table[ids[row]];  w_n = 1 (one number for all channels) or W */
+int lia_embed_rmsnorm(const int64_t* ids, const void* table, int table_f32, const float* w, int w_n, float* x, int rows, int W,
+                      int vocab, float eps, lia_stream_t stream);
+/* y != NULL: x += w_post * y / rms(y) (norm after a sublayer + residual sum);  h != NULL: h = w_pre * x / rms(x) */
+int lia_rms_add_norm(float* x, const void* y, int y_f32, const float* w_post, int w_post_n, const float* w_pre, int w_pre_n,
+                     void* h, int h_f32, int rows, int W, float eps, lia_stream_t stream);
+/* h[r] = w * x[rows[r]] / rms(x[rows[r]]) for n selected rows */
+int lia_rms_gather(const float* x, const int* rows, const float* w, int w_n, void* h, int h_f32, int n, int W, float eps,
+                   lia_stream_t stream);
+/* out = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up rows hold gate at column 0 and up at column up_off */
+int lia_clamped_glu(const void* gate_up, int ld, int up_off, void* out, int act_f32, int M, int F, float limit, float alpha, lia_stream_t stream);
+/* out[m][n] = act(a[m] . w[n] + bias[n]), N small (per-head gates), fp32 out.  mode 0: identity; 1: first N/2 outputs
+ * cap*tanh(z/cap), last N/2 logsigmoid(cap*tanh(z/cap)) (log input / log forget gates); 2: sigmoid */
+int lia_linear_small(const void* a, int a_f32, int lda, const void* w, int w_f32, const float* bias, float* out, int M, int N, int K,
+                     int mode, float cap, lia_stream_t stream);
+/* C[b][m][n] = scale * sum_k A[b][m][k] W[b][n][k] on the CUDA cores, fp32 products and sums; element strides */
+int lia_linear_plain(const void* A, int a_f32, long long lda, long long sA, const void* W, int w_f32, long long ldw, long long sW,
+                     void* C, int c_f32, long long ldc, long long sC, int M, int N, int K, int batch, float scale, lia_stream_t stream);
+int lia_argmax_f32(const float* logits, int64_t* next, int B, int V, int suppress_id, lia_stream_t stream);
+/* matrix-memory recurrence over every portion of the step; q/k [rows][H*dim], v [rows][H*vdim] with row stride ld;
+ * gates [rows][2H] = log input gates then log forget gates; state_S [slots][H][vdim][dim], state_n [slots][H][dim],
+ * state_m [slots][H]; o [rows][H*vdim] = S^T q / (max(|n.q|, exp(-m)) + den_eps) */
+int lia_mlstm_scan(const void* q, const void* k, const void* v, int act_f32, int ld, const float* gates, float* state_S, float* state_n,
+                   float* state_m, const int* segs, int nseg, int H, int dim, int vdim, float q_scale, float den_eps, float* o,
+                   lia_stream_t stream);
+/* out[row][h] = o[row][h] / rms_over_vdim * w[h] * sigmoid(gate[row][h]) */
+int lia_headnorm_gate(const float* o, const float* w, const void* gate, int ldg, void* out, int act_f32, int M, int H, int vdim, float eps,
+                      lia_stream_t stream);
+/* cache[slot][pos] = [rmsnorm(dkv[:kv_rank]) * c_norm_w | rotate(dkv[kv_rank:], pos)];  qa[row][h][kv_rank:] =
+ * rotate(q[row][h][dim:], pos)  (qa rows are [H][kv_rank + rot] fp32; the caller fills qa[..][:kv_rank]) */
+int lia_latent_prep(const void* q, int ldq, const void* dkv, int ldd, int act_f32, const float* c_norm_w, const float* inv_freq,
+                    const int* meta, void* cache, long long slot_stride, float* qa, int M, int H, int dim, int rot, int rot_dims,
+                    int kv_rank, float eps, lia_stream_t stream);
+/* out[row][h] = gate[row][h] * sum_{s <= pos(row)} softmax_s((qa[row][h] . cache[slot][s]) * scale) cache[slot][s][:kv_rank]
+ * (gate may be NULL: no output gate) */
+int lia_latent_attn(const float* qa, const void* cache, int cache_f32, long long slot_stride, const int* meta, const float* gate,
+                    float* out, int M, int H, int kv_rank, int rot, float scale, lia_stream_t stream);
 
 #ifdef __cplusplus
 }

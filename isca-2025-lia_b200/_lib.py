@@ -6,13 +6,13 @@ if the shared library is missing or a call fails, this module raises.
 """
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_longlong, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libliab200.so")
 
 EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_RESIDUAL, EPI_QKV = 0, 1, 2, 3
-ABI_VERSION = 5
+ABI_VERSION = 6
 TP_MAX_WORLD = 8
 P2P_HANDLE_BYTES = 64
 
@@ -83,6 +83,23 @@ _PROTOTYPES = {
     "lia_program_error": (c_int, [c_void_p]),
     "lia_program_num_ops": (c_int, [c_void_p]),
     "lia_program_destroy": (c_int, [c_void_p]),
+    # models with a 32-bit residual stream, matrix-memory mixers and latent-cache attention
+    "lia_embed_rmsnorm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_rms_add_norm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                                 c_void_p]),
+    "lia_rms_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_clamped_glu": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p]),
+    "lia_linear_small": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                 c_void_p]),
+    "lia_linear_plain": (c_int, [c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int,
+                                 c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_argmax_f32": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "lia_mlstm_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p]),
+    "lia_headnorm_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_latent_prep": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_latent_attn": (c_int, [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
 }
 
 EXPORTS = tuple(_PROTOTYPES)

@@ -1,0 +1,212 @@
+// Matrix-memory recurrence (mLSTM) with a running-maximum stabiliser, for prompts, portions of prompts and single decoded
+// tokens alike.  Per head, with log gates i_t, f_t (already capped / log-sigmoided by the gate projection's epilogue):
+//     m_t = max(f_t + m_{t-1}, i_t)
+//     S_t = exp(f_t + m_{t-1} - m_t) S_{t-1} + exp(i_t - m_t) k_t v_t^T          (dim x vdim)
+//     n_t = exp(f_t + m_{t-1} - m_t) n_{t-1} + exp(i_t - m_t) k_t
+//     o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + den_eps)
+// State (S, n, m) is fp32 and lives per sequence slot; S is stored transposed, [slot][head][vdim][dim], so that the
+// dim-long column a warp owns is contiguous.  Everything here is fp32 arithmetic on the CUDA cores; q, k, v arrive as the
+// projection wrote them (bf16 or fp32).
+//
+// Work split: a warp owns CW = 4 columns of S (4 value channels) of one head of one sequence and keeps them in registers
+// for the whole portion; lane l owns rows l, l+32, ...  A token costs the warp DR*CW*2 FMAs per lane and one butterfly
+// reduction of CW+1 partial dot products; nothing is synchronised per token.  The 4 warps of a block share q, k and the
+// gates of their head through a double-buffered shared-memory stage of TB = 8 tokens that is fetched while the previous
+// 8 tokens are processed.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int TB = 8;            // tokens per stage
+constexpr int CW = 4;            // columns of S per warp
+constexpr int NW = 4;            // warps per block
+constexpr int CB = CW * NW;      // columns per block
+
+// segs[s] = {slot, first position, first row, rows} of portion s
+template <typename T, int DR>
+__global__ void __launch_bounds__(NW * 32) mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
+                                                             const float* __restrict__ gates, float* __restrict__ St, float* __restrict__ nst,
+                                                             float* __restrict__ mst, const int* __restrict__ segs, int H, int dim, int vdim,
+                                                             float q_scale, float den_eps, float* __restrict__ o) {
+  constexpr int DP = DR * 32;                    // dim padded to whole warps
+  constexpr int ROWF = 2 * DP + CB + 2;          // floats of one staged token: q | k | v (this block's columns) | i | f
+  constexpr int NST = (TB * ROWF + NW * 32 - 1) / (NW * 32);
+  extern __shared__ float stage[];               // [2][TB][ROWF]
+  const int seg = blockIdx.z, h = blockIdx.y, colb = blockIdx.x * CB;
+  const int slot = segs[4 * seg], row0 = segs[4 * seg + 2], len = segs[4 * seg + 3];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col0 = colb + warp * CW;
+
+  float S[DR][CW], n[DR];
+  float* Sp = St + ((size_t)slot * H + h) * vdim * dim;
+  float* np = nst + ((size_t)slot * H + h) * dim;
+#pragma unroll
+  for (int i = 0; i < DR; ++i) {
+    const int r = lane + 32 * i;
+    n[i] = r < dim ? np[r] : 0.f;
+#pragma unroll
+    for (int c = 0; c < CW; ++c) S[i][c] = (r < dim && col0 + c < vdim) ? Sp[(size_t)(col0 + c) * dim + r] : 0.f;
+  }
+  float m = mst[(size_t)slot * H + h];
+
+  float buf[NST];
+  // fetch the inputs of tokens [g*TB, g*TB+TB) of the portion into registers
+  auto fetch = [&](int g) {
+#pragma unroll
+    for (int s = 0; s < NST; ++s) {
+      const int e = threadIdx.x + s * NW * 32;
+      float val = 0.f;
+      if (e < TB * ROWF) {
+        const int t = e / ROWF, j = e - t * ROWF;
+        const int tok = g * TB + t;
+        if (tok < len) {
+          const size_t row = (size_t)(row0 + tok);
+          if (j < DP) {
+            if (j < dim) val = ldf(q + row * ld + h * dim + j) * q_scale;
+          } else if (j < 2 * DP) {
+            if (j - DP < dim) val = ldf(k + row * ld + h * dim + (j - DP));
+          } else if (j < 2 * DP + CB) {
+            const int c = colb + j - 2 * DP;
+            if (c < vdim) val = ldf(v + row * ld + h * vdim + c);
+          } else {
+            val = gates[row * 2 * H + (j - 2 * DP - CB) * H + h];
+          }
+        }
+      }
+      buf[s] = val;
+    }
+  };
+  auto put = [&](int b) {
+#pragma unroll
+    for (int s = 0; s < NST; ++s) {
+      const int e = threadIdx.x + s * NW * 32;
+      if (e < TB * ROWF) stage[b * TB * ROWF + e] = buf[s];
+    }
+  };
+
+  const int groups = (len + TB - 1) / TB;
+  fetch(0);
+  put(0);
+  __syncthreads();
+  for (int g = 0; g < groups; ++g) {
+    if (g + 1 < groups) fetch(g + 1);            // in flight while this group is processed
+    const float* st = stage + (g & 1) * TB * ROWF;
+    const int nt = min(TB, len - g * TB);
+    for (int t = 0; t < nt; ++t) {
+      const float* tk = st + t * ROWF;
+      const float ig = tk[2 * DP + CB], fg = tk[2 * DP + CB + 1];
+      const float m_new = fmaxf(fg + m, ig);
+      const float a = expf(fg + m - m_new), b = expf(ig - m_new);
+      float part[CW + 1];
+#pragma unroll
+      for (int c = 0; c <= CW; ++c) part[c] = 0.f;
+#pragma unroll
+      for (int i = 0; i < DR; ++i) {
+        const float qv = tk[lane + 32 * i], kv = tk[DP + lane + 32 * i];
+        const float bk = b * kv;
+        n[i] = fmaf(a, n[i], bk);
+        part[CW] = fmaf(n[i], qv, part[CW]);
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+          S[i][c] = fmaf(a, S[i][c], bk * tk[2 * DP + warp * CW + c]);
+          part[c] = fmaf(S[i][c], qv, part[c]);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c <= CW; ++c) part[c] = warp_sum(part[c]);
+      const float den = fmaxf(fabsf(part[CW]), expf(-m_new)) + den_eps;
+      m = m_new;
+      float mine = part[0];
+#pragma unroll
+      for (int c = 1; c < CW; ++c) mine = (lane == c) ? part[c] : mine;
+      if (lane < CW && col0 + lane < vdim) o[(size_t)(row0 + g * TB + t) * H * vdim + h * vdim + col0 + lane] = mine / den;
+    }
+    if (g + 1 < groups) put((g + 1) & 1);        // the other buffer: last read two groups ago, before the barrier below
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < DR; ++i) {
+    const int r = lane + 32 * i;
+    if (r < dim) {
+      if (colb == 0 && warp == 0) np[r] = n[i];
+#pragma unroll
+      for (int c = 0; c < CW; ++c)
+        if (col0 + c < vdim) Sp[(size_t)(col0 + c) * dim + r] = S[i][c];
+    }
+  }
+  if (colb == 0 && threadIdx.x == 0) mst[(size_t)slot * H + h] = m;
+}
+
+// out[row][h][c] = o / sqrt(mean_c(o^2) + eps) * w[h*vdim + c] * sigmoid(gate[row][h*vdim + c]); one warp per (row, head)
+template <typename T>
+__global__ void __launch_bounds__(128) headnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, const T* __restrict__ gate, int ldg,
+                                                            T* __restrict__ out, int M, int H, int vdim, float eps) {
+  const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (pair >= M * H) return;
+  const int row = pair / H, h = pair - row * H;
+  const float* orow = o + (size_t)row * H * vdim + h * vdim;
+  float ss = 0.f;
+  for (int c = lane; c < vdim; c += 32) ss += orow[c] * orow[c];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+  for (int c = lane; c < vdim; c += 32) {
+    const float g = ldf(gate + (size_t)row * ldg + h * vdim + c);
+    stf(out + (size_t)row * H * vdim + h * vdim + c, orow[c] * inv * w[h * vdim + c] * (1.0f / (1.0f + expf(-g))));
+  }
+}
+
+template <typename T, int DR>
+int launch_scan(const void* q, const void* k, const void* v, int ld, const float* gates, float* St, float* nst, float* mst, const int* segs,
+                int nseg, int H, int dim, int vdim, float q_scale, float den_eps, float* o, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * TB * (2 * DR * 32 + CB + 2) * sizeof(float);
+  if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<T, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((vdim + CB - 1) / CB, H, nseg);
+  mlstm_scan_kernel<T, DR><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), reinterpret_cast<const T*>(v),
+                                                            ld, gates, St, nst, mst, segs, H, dim, vdim, q_scale, den_eps, o);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+template <typename T>
+int dispatch_scan(const void* q, const void* k, const void* v, int ld, const float* gates, float* St, float* nst, float* mst, const int* segs,
+                  int nseg, int H, int dim, int vdim, float q_scale, float den_eps, float* o, cudaStream_t stream) {
+  if (dim <= 32) return launch_scan<T, 1>(q, k, v, ld, gates, St, nst, mst, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+  if (dim <= 64) return launch_scan<T, 2>(q, k, v, ld, gates, St, nst, mst, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+  if (dim <= 128) return launch_scan<T, 4>(q, k, v, ld, gates, St, nst, mst, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+  if (dim <= 256) return launch_scan<T, 8>(q, k, v, ld, gates, St, nst, mst, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+  return launch_scan<T, 16>(q, k, v, ld, gates, St, nst, mst, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+}
+
+}  // namespace
+
+extern "C" int lia_mlstm_scan(const void* q, const void* k, const void* v, int act_f32, int ld, const float* gates, float* state_S,
+                              float* state_n, float* state_m, const int* segs, int nseg, int H, int dim, int vdim, float q_scale,
+                              float den_eps, float* o, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(q && k && v && gates && state_S && state_n && state_m && segs && o, "lia_mlstm_scan: null pointer");
+  LIA_CHECK_ARG(nseg > 0 && nseg <= 65535 && H > 0 && H <= 65535 && dim > 0 && dim <= 512 && vdim > 0, "lia_mlstm_scan: bad shape nseg=%d H=%d dim=%d vdim=%d", nseg, H, dim, vdim);
+  if (act_f32) return dispatch_scan<float>(q, k, v, ld, gates, state_S, state_n, state_m, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+  return dispatch_scan<bf16>(q, k, v, ld, gates, state_S, state_n, state_m, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+}
+
+extern "C" int lia_headnorm_gate(const float* o, const float* w, const void* gate, int ldg, void* out, int act_f32, int M, int H, int vdim,
+                                 float eps, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(o && w && gate && out && M > 0 && H > 0 && vdim > 0 && ldg >= H * vdim, "lia_headnorm_gate: bad arguments");
+  const long long pairs = (long long)M * H;
+  const unsigned grid = (unsigned)((pairs + 3) / 4);
+  if (act_f32) headnorm_gate_kernel<float><<<grid, 128, 0, stream>>>(o, w, reinterpret_cast<const float*>(gate), ldg, reinterpret_cast<float*>(out), M, H, vdim, eps);
+  else headnorm_gate_kernel<bf16><<<grid, 128, 0, stream>>>(o, w, reinterpret_cast<const bf16*>(gate), ldg, reinterpret_cast<bf16*>(out), M, H, vdim, eps);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}

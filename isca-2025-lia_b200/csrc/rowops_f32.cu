@@ -1,0 +1,338 @@
+// Row operations of models that keep their residual stream in 32-bit floats: RMS norms with a scalar or a per-channel
+// weight (fused with the residual add that follows a sublayer and with the norm that precedes the next one), the token
+// embedding with its norm, a gated feed-forward activation with clamps, a projection onto a handful of outputs with the
+// gate non-linearities in its epilogue, a plain strided-batched projection on the CUDA cores (true 32-bit products and
+// sums: the exact path, and the carrier of shapes the tensor-core GEMM does not take), and a 32-bit argmax.
+//
+// Activations are bf16 or fp32 (`act_f32`); everything a norm, a gate or the residual sum computes is fp32 either way.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// sum over a block of NT threads; every thread gets the result.  `red` holds NT/32 floats.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();                       // `red` may still be read from the previous call
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < NT / 32; ++w) s += red[w];
+  return s;
+}
+
+// x[row] = w * e / sqrt(mean(e^2) + eps), e = table[ids[row]]
+template <typename T>
+__global__ void __launch_bounds__(256) embed_rmsnorm_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table,
+                                                            const float* __restrict__ w, int w_n, float* __restrict__ x, int W,
+                                                            int vocab, float eps) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  long long id = ids[row];
+  if (id < 0 || id >= vocab) id = 0;     // the host checks the range; never read outside the table
+  const T* e = table + (size_t)id * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += 256) {
+    const float v = ldf(e + i);
+    ss += v * v;
+  }
+  ss = block_sum<256>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 256) x[(size_t)row * W + i] = ldf(e + i) * inv * w[w_n == 1 ? 0 : i];
+}
+
+// if y:  x[row] += w_post * y / sqrt(mean(y^2) + eps)          (the norm after a sublayer, then the residual sum)
+// if h:  h[row]  = w_pre  * x / sqrt(mean(x^2) + eps)          (the norm before the next sublayer)
+// `xs` (dynamic shared memory, W floats) keeps the updated row between the two.
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(256) rms_add_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ w_post,
+                                                           int w_post_n, const float* __restrict__ w_pre, int w_pre_n, TH* __restrict__ h,
+                                                           int W, float eps) {
+  extern __shared__ float xs[];
+  __shared__ float red[8];
+  const size_t base = (size_t)blockIdx.x * W;
+  if (y != nullptr) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += 256) {
+      const float v = ldf(y + base + i);
+      ss += v * v;
+    }
+    ss = block_sum<256>(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += 256) {
+      const float v = x[base + i] + ldf(y + base + i) * inv * w_post[w_post_n == 1 ? 0 : i];
+      x[base + i] = v;
+      xs[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += 256) xs[i] = x[base + i];
+  }
+  if (h == nullptr) return;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += 256) ss += xs[i] * xs[i];      // each thread re-reads only what it wrote
+  ss = block_sum<256>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 256) stf(h + base + i, xs[i] * inv * w_pre[w_pre_n == 1 ? 0 : i]);
+}
+
+// h[r] = w * x[rows[r]] / sqrt(mean^2 + eps): the norm of a few selected rows (the positions whose logits are asked for)
+template <typename TH>
+__global__ void __launch_bounds__(256) rms_gather_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                                                         int w_n, TH* __restrict__ h, int W, float eps) {
+  __shared__ float red[8];
+  const size_t src = (size_t)rows[blockIdx.x] * W, dst = (size_t)blockIdx.x * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += 256) ss += x[src + i] * x[src + i];
+  ss = block_sum<256>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 256) stf(h + dst + i, x[src + i] * inv * w[w_n == 1 ? 0 : i]);
+}
+
+// out = g * sigmoid(alpha * g) * (u + 1),  g = min(gate, limit), u = clamp(up, -limit, limit); gate | up are the two
+// column ranges of one projection's output row (row stride ld; up starts at column up_off)
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, int ld, int up_off, T* __restrict__ out, int M, int F, float limit, float alpha) {
+  const size_t n = (size_t)M * F;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = e / F;
+    const int f = (int)(e - m * F);
+    const float g = fminf(ldf(gu + m * ld + f), limit);
+    const float u = fminf(fmaxf(ldf(gu + m * ld + up_off + f), -limit), limit);
+    stf(out + e, g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+  }
+}
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// out[m][n] = act(sum_k a[m][k] w[n][k] + bias[n]) for a handful of outputs (gates: one per head), fp32 out.
+// mode 0: identity; 1: n < N/2 -> cap*tanh(z/cap), n >= N/2 -> logsigmoid(cap*tanh(z/cap)); 2: sigmoid.
+// One warp per row; 8 outputs per sweep over the row.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128) linear_small_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, const float* __restrict__ bias,
+                                                           float* __restrict__ out, int M, int N, int K, int mode, float cap) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const TA* ar = a + (size_t)row * lda;
+  for (int n0 = 0; n0 < N; n0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float av = ldf(ar + k);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (n0 + j < N) acc[j] = fmaf(av, ldf(w + (size_t)(n0 + j) * K + k), acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = warp_sum(acc[j]);
+      const int n = n0 + j;
+      if (lane == 0 && n < N) {
+        float z = s + (bias ? bias[n] : 0.f);
+        if (mode == 1) {
+          z = cap * tanhf(z / cap);
+          if (n >= N / 2) z = log_sigmoid(z);
+        } else if (mode == 2) {
+          z = 1.0f / (1.0f + expf(-z));
+        }
+        out[(size_t)row * N + n] = z;
+      }
+    }
+  }
+}
+
+// C[b][m][n] = scale * sum_k A[b][m][k] * W[b][n][k]; 64 x 64 tile per block, 16-wide k slabs, 4 x 4 outputs per thread,
+// fp32 products and sums in k order.
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) linear_plain_kernel(const TA* __restrict__ A, long long lda, long long sA, const TW* __restrict__ Wt,
+                                                           long long ldw, long long sW, TC* __restrict__ C, long long ldc, long long sC, int M,
+                                                           int N, int K, float scale) {
+  __shared__ float As[16][64 + 4];
+  __shared__ float Ws[16][64 + 4];
+  const int b = blockIdx.z;
+  A += (size_t)b * sA;
+  Wt += (size_t)b * sW;
+  C += (size_t)b * sC;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int r = e >> 4, kk = e & 15;
+      const int k = k0 + kk;
+      As[kk][r] = (m0 + r < M && k < K) ? ldf(A + (size_t)(m0 + r) * lda + k) : 0.f;
+      Ws[kk][r] = (n0 + r < N && k < K) ? ldf(Wt + (size_t)(n0 + r) * ldw + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wv[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < M && n < N) stf(C + (size_t)m * ldc + n, acc[i][j] * scale);
+    }
+}
+
+__global__ void __launch_bounds__(256) argmax_f32_kernel(const float* __restrict__ logits, int64_t* __restrict__ next, int V, int suppress) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const float* row = logits + (size_t)blockIdx.x * V;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int idx = threadIdx.x; idx < V; idx += 256) {
+    const float v = (idx == suppress) ? -INFINITY : row[idx];
+    if (v > best || (v == best && idx < bi)) { best = v; bi = idx; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    next[blockIdx.x] = bi;
+  }
+}
+
+template <typename TA, typename TW>
+int launch_plain(const void* A, long long lda, long long sA, const void* W, long long ldw, long long sW, void* C, long long ldc, long long sC,
+                 int M, int N, int K, int batch, float scale, int c_f32, cudaStream_t stream) {
+  dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
+  if (c_f32)
+    linear_plain_kernel<TA, TW, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const TA*>(A), lda, sA, reinterpret_cast<const TW*>(W), ldw, sW,
+                                                                 reinterpret_cast<float*>(C), ldc, sC, M, N, K, scale);
+  else
+    linear_plain_kernel<TA, TW, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const TA*>(A), lda, sA, reinterpret_cast<const TW*>(W), ldw, sW,
+                                                                reinterpret_cast<bf16*>(C), ldc, sC, M, N, K, scale);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+}  // namespace
+
+extern "C" int lia_embed_rmsnorm(const int64_t* ids, const void* table, int table_f32, const float* w, int w_n, float* x, int rows,
+                                 int W, int vocab, float eps, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(ids && table && w && x, "lia_embed_rmsnorm: null pointer");
+  LIA_CHECK_ARG(rows > 0 && W > 0 && vocab > 0 && (w_n == 1 || w_n == W), "lia_embed_rmsnorm: bad shape rows=%d W=%d w_n=%d", rows, W, w_n);
+  if (table_f32)
+    embed_rmsnorm_kernel<float><<<rows, 256, 0, stream>>>(ids, reinterpret_cast<const float*>(table), w, w_n, x, W, vocab, eps);
+  else
+    embed_rmsnorm_kernel<bf16><<<rows, 256, 0, stream>>>(ids, reinterpret_cast<const bf16*>(table), w, w_n, x, W, vocab, eps);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_rms_add_norm(float* x, const void* y, int y_f32, const float* w_post, int w_post_n, const float* w_pre, int w_pre_n,
+                                void* h, int h_f32, int rows, int W, float eps, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(x && (y || h), "lia_rms_add_norm: nothing to do");
+  LIA_CHECK_ARG(!y || (w_post && (w_post_n == 1 || w_post_n == W)), "lia_rms_add_norm: bad weight of the norm after the sublayer");
+  LIA_CHECK_ARG(!h || (w_pre && (w_pre_n == 1 || w_pre_n == W)), "lia_rms_add_norm: bad weight of the norm before the sublayer");
+  LIA_CHECK_ARG(rows > 0 && W > 0 && (size_t)W * 4 <= 160 * 1024, "lia_rms_add_norm: bad shape rows=%d W=%d", rows, W);
+  const size_t smem = (size_t)W * sizeof(float);
+#define LIA_RAN(TY, TH)                                                                                                      \
+  do {                                                                                                                       \
+    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(rms_add_norm_kernel<TY, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    rms_add_norm_kernel<TY, TH><<<rows, 256, smem, stream>>>(x, reinterpret_cast<const TY*>(y), w_post, w_post_n, w_pre, w_pre_n,        \
+                                                             reinterpret_cast<TH*>(h), W, eps);                              \
+  } while (0)
+  if (y_f32 && h_f32) LIA_RAN(float, float);
+  else if (y_f32) LIA_RAN(float, bf16);
+  else if (h_f32) LIA_RAN(bf16, float);
+  else LIA_RAN(bf16, bf16);
+#undef LIA_RAN
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_rms_gather(const float* x, const int* rows, const float* w, int w_n, void* h, int h_f32, int n, int W, float eps,
+                              lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(x && rows && w && h && n > 0 && W > 0 && (w_n == 1 || w_n == W), "lia_rms_gather: bad arguments");
+  if (h_f32) rms_gather_kernel<float><<<n, 256, 0, stream>>>(x, rows, w, w_n, reinterpret_cast<float*>(h), W, eps);
+  else rms_gather_kernel<bf16><<<n, 256, 0, stream>>>(x, rows, w, w_n, reinterpret_cast<bf16*>(h), W, eps);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_clamped_glu(const void* gate_up, int ld, int up_off, void* out, int act_f32, int M, int F, float limit, float alpha,
+                               lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(gate_up && out && M > 0 && F > 0 && up_off >= F && ld >= up_off + F, "lia_clamped_glu: bad arguments");
+  const size_t n = (size_t)M * F;
+  size_t blocks = (n + 255) / 256;
+  const size_t capb = (size_t)lia_sm_count() * 16;
+  if (blocks > capb) blocks = capb;
+  if (act_f32) clamped_glu_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(gate_up), ld, up_off, reinterpret_cast<float*>(out), M, F, limit, alpha);
+  else clamped_glu_kernel<bf16><<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(gate_up), ld, up_off, reinterpret_cast<bf16*>(out), M, F, limit, alpha);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_linear_small(const void* a, int a_f32, int lda, const void* w, int w_f32, const float* bias, float* out, int M, int N,
+                                int K, int mode, float cap, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(a && w && out && M > 0 && N > 0 && K > 0 && lda >= K, "lia_linear_small: bad arguments");
+  LIA_CHECK_ARG(mode >= 0 && mode <= 2 && (mode != 1 || (N % 2 == 0 && cap > 0.f)), "lia_linear_small: bad mode %d (N=%d cap=%f)", mode, N, cap);
+  const int grid = (M + 3) / 4;
+  if (a_f32 && w_f32) linear_small_kernel<float, float><<<grid, 128, 0, stream>>>(reinterpret_cast<const float*>(a), lda, reinterpret_cast<const float*>(w), bias, out, M, N, K, mode, cap);
+  else if (a_f32) linear_small_kernel<float, bf16><<<grid, 128, 0, stream>>>(reinterpret_cast<const float*>(a), lda, reinterpret_cast<const bf16*>(w), bias, out, M, N, K, mode, cap);
+  else if (w_f32) linear_small_kernel<bf16, float><<<grid, 128, 0, stream>>>(reinterpret_cast<const bf16*>(a), lda, reinterpret_cast<const float*>(w), bias, out, M, N, K, mode, cap);
+  else linear_small_kernel<bf16, bf16><<<grid, 128, 0, stream>>>(reinterpret_cast<const bf16*>(a), lda, reinterpret_cast<const bf16*>(w), bias, out, M, N, K, mode, cap);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_linear_plain(const void* A, int a_f32, long long lda, long long sA, const void* W, int w_f32, long long ldw, long long sW,
+                                void* C, int c_f32, long long ldc, long long sC, int M, int N, int K, int batch, float scale,
+                                lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(A && W && C && M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535, "lia_linear_plain: bad arguments");
+  LIA_CHECK_ARG(lda >= K && ldw >= K && ldc >= N, "lia_linear_plain: leading dimensions smaller than the rows");
+  LIA_CHECK_ARG((M + 63) / 64 <= 65535, "lia_linear_plain: too many rows (%d)", M);
+  if (a_f32 && w_f32) return launch_plain<float, float>(A, lda, sA, W, ldw, sW, C, ldc, sC, M, N, K, batch, scale, c_f32, stream);
+  if (a_f32) return launch_plain<float, bf16>(A, lda, sA, W, ldw, sW, C, ldc, sC, M, N, K, batch, scale, c_f32, stream);
+  if (w_f32) return launch_plain<bf16, float>(A, lda, sA, W, ldw, sW, C, ldc, sC, M, N, K, batch, scale, c_f32, stream);
+  return launch_plain<bf16, bf16>(A, lda, sA, W, ldw, sW, C, ldc, sC, M, N, K, batch, scale, c_f32, stream);
+}
+
+extern "C" int lia_argmax_f32(const float* logits, int64_t* next, int B, int V, int suppress_id, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(logits && next && B > 0 && V > 0, "lia_argmax_f32: bad arguments");
+  argmax_f32_kernel<<<B, 256, 0, stream>>>(logits, next, V, suppress_id);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}

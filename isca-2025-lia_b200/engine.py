@@ -1,0 +1,140 @@
+"""Step-wise serving engine: requests that come and go, prompts fed in portions, decoded tokens one by one, several
+requests per step.
+
+``Engine.step(entries, end)`` is the one step function: every entry brings the next tokens of a request (a whole prompt,
+a portion of one, or a single decoded token) and the places among them whose logits are wanted; the engine gives a new
+request a slot of the model's per-sequence state (seq_state.SlotState), lays the entries' tokens out as the rows of one
+batch, cuts what exceeds the row budget into further passes, runs the model's ``forward_rows`` and frees the slots of the
+requests named in ``end``.  ``Engine.generate`` is greedy decoding on top of it (argmax on the device); the trace runner
+(bin/trace_run) drives the same ``step``.
+
+The reference serves one static batch per generate() call (greedy_search.py:37-460); this is the request-level face the
+step-wise models need.
+"""
+import numpy as np
+import torch
+
+from . import ops
+from .seq_layers import StepBatch
+
+
+class Engine:
+    def __init__(self, model, max_tokens, max_requests=4, max_rows=4096):
+        self.model = model
+        self.max_rows = int(max_rows)
+        self.slots = model.new_state(int(max_requests), int(max_tokens))
+        self.device = model.device
+        self._host = self._copied = None
+
+    # ---- batch assembly: one pinned staging buffer, one H2D copy per pass
+    def _upload(self, ids, segs, meta, want):
+        n_ids, n_seg, n_meta, n_want = len(ids), len(segs) * 4, len(meta) * 2, len(want)
+        words = 2 * n_ids + n_seg + n_meta + n_want
+        if self._host is None or self._host.numel() < words:
+            self._host = torch.empty(max(2 * words, 1024), dtype=torch.int32).pin_memory()
+            self._copied = torch.cuda.Event()
+        else:
+            self._copied.synchronize()                     # the previous pass's copy has left the staging buffer
+        host = self._host[:max(words, 2)]
+        a = host.numpy()
+        a[:2 * n_ids].view(np.int64)[:] = np.asarray(ids, dtype=np.int64)
+        o = 2 * n_ids
+        a[o:o + n_seg] = np.asarray(segs, dtype=np.int32).reshape(-1)
+        a[o + n_seg:o + n_seg + n_meta] = np.asarray(meta, dtype=np.int32).reshape(-1)
+        if n_want:
+            a[o + n_seg + n_meta:words] = np.asarray(want, dtype=np.int32)
+        dev = host.to(self.device, non_blocking=True)
+        self._copied.record()
+        d_ids = dev[:2 * n_ids].view(torch.int64)
+        d_segs = dev[o:o + n_seg].view(-1, 4)
+        d_meta = dev[o + n_seg:o + n_seg + n_meta].view(-1, 2)
+        d_want = dev[o + n_seg + n_meta:words] if n_want else None
+        return d_ids, StepBatch(n_ids, d_segs, d_meta), d_want
+
+    def _passes(self, entries):
+        """Cut the step's entries into passes of at most ``max_rows`` rows; an entry longer than the budget continues in
+        the next pass (its state carries over, exactly as between steps)."""
+        cur, rows = [], 0
+        for slot, tokens, want in entries:
+            at = 0
+            while at < len(tokens):
+                take = min(len(tokens) - at, self.max_rows - rows)
+                cur.append((slot, tokens[at:at + take], [w - at for w in want if at <= w < at + take]))
+                rows += take
+                at += take
+                if rows == self.max_rows:
+                    yield cur
+                    cur, rows = [], 0
+        if cur:
+            yield cur
+
+    def step(self, entries, end=(), trace=None):
+        """entries: dicts ``{"id", "tokens", "want"}``; returns fp32 logits [wanted places, vocab] in the order of the entries
+        and of their ``want`` lists (None if nothing is wanted)."""
+        vocab = self.model.config.vocab
+        todo = []
+        for e in entries:
+            toks = [int(t) for t in e["tokens"]]
+            if not toks:
+                continue
+            if min(toks) < 0 or max(toks) >= vocab:
+                raise ValueError(f"request {e['id']!r}: token id outside [0, {vocab})")
+            want = sorted(int(w) for w in e.get("want", ()))
+            if want and (want[0] < 0 or want[-1] >= len(toks)):
+                raise ValueError(f"request {e['id']!r}: wanted place outside its {len(toks)} tokens")
+            slot = self.slots.slot_of(e["id"])
+            if slot is None:
+                slot = self.slots.alloc(e["id"])
+            todo.append((slot, toks, want))
+        outs = []
+        for group in self._passes(todo):
+            ids, segs, meta, want, row = [], [], [], [], 0
+            for slot, toks, w in group:
+                p0 = self.slots.reserve(slot, len(toks))
+                segs.append((slot, p0, row, len(toks)))
+                meta += [(slot, p0 + i) for i in range(len(toks))]
+                want += [row + i for i in w]
+                ids += toks
+                row += len(toks)
+            d_ids, batch, d_want = self._upload(ids, segs, meta, want)
+            logits = self.model.forward_rows(d_ids, batch, d_want, self.slots, trace=trace)
+            if logits is not None:
+                outs.append(logits)
+        for rid in end:
+            if self.slots.slot_of(rid) is not None:
+                self.slots.free(rid)
+        if not outs:
+            return None
+        return outs[0] if len(outs) == 1 else torch.cat(outs, 0)
+
+    def generate(self, prompts, max_new_tokens, chunk=None, suppress_id=-1):
+        """Greedy decoding of ``prompts`` (lists of ids, any lengths) as one batch: prompts in portions of ``chunk`` tokens
+        (None: whole), then one token per request per step.  Returns prompt + new tokens per request."""
+        ids = list(range(len(prompts)))
+        done = [0] * len(prompts)
+        out = [list(p) for p in prompts]
+        longest = max(len(p) for p in prompts)
+        portion = chunk or longest
+        nxt = [None] * len(prompts)
+        while any(d < len(p) for d, p in zip(done, prompts)):
+            entries = []
+            for i, p in enumerate(prompts):
+                if done[i] < len(p):
+                    t = p[done[i]:done[i] + portion]
+                    last = done[i] + len(t) == len(p)
+                    entries.append({"id": i, "tokens": t, "want": [len(t) - 1] if last else []})
+                    done[i] += len(t)
+            logits = self.step(entries)
+            if logits is not None:
+                picks = ops.argmax_f32(logits, suppress_id).tolist()
+                for e, tok in zip([e for e in entries if e["want"]], picks):
+                    nxt[e["id"]] = tok
+        for i in ids:
+            out[i].append(nxt[i])
+        for _ in range(max_new_tokens - 1):
+            logits = self.step([{"id": i, "tokens": [out[i][-1]], "want": [0]} for i in ids])
+            for i, tok in zip(ids, ops.argmax_f32(logits, suppress_id).tolist()):
+                out[i].append(tok)
+        for i in ids:
+            self.slots.free(i)
+        return out

@@ -263,3 +263,184 @@ def residual_add(x, residual, out=None):
           "lia_residual_add_bf16")
     count_launches()
     return out
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Models with a 32-bit residual stream, matrix-memory (mLSTM) mixers and latent-cache attention.  Activations are bf16
+# or fp32 tensors; norm weights, gates, recurrent state and the residual stream are fp32.  (The reference has no such
+# models: its one family is OPT.)
+# ------------------------------------------------------------------------------------------------------------------
+F32 = torch.float32
+
+
+def _f32(t):
+    """1 for an fp32 tensor, 0 for bf16; anything else is refused."""
+    if t.dtype == F32:
+        return 1
+    if t.dtype == BF16:
+        return 0
+    raise _lib.LiaError(f"need a bf16 or fp32 tensor, got {t.dtype}")
+
+
+def _dev(t, name, dtype=None):
+    if not t.is_cuda or (dtype is not None and t.dtype != dtype):
+        raise _lib.LiaError(f"{name}: need a CUDA {dtype or ''} tensor, got {t.dtype} on {t.device}")
+    return t
+
+
+def _rowmajor(t, name):
+    """A 2-D view whose rows are contiguous (column slices of a wider buffer are fine): returns its row stride."""
+    _dev(t, name)
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise _lib.LiaError(f"{name}: need a 2-D tensor with unit column stride, got {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+def embed_rmsnorm(ids, table, w, x, eps):
+    """x[r] = w * e / sqrt(mean(e^2) + eps) with e = table[ids[r]]: the token embedding followed by the model's norm."""
+    _req(ids, "ids", torch.int64); _req(w, "w", F32); _req(x, "x", F32); _dev(table, "table")
+    rows, W = x.shape
+    check(_lib.load().lia_embed_rmsnorm(_p(ids), _p(table.contiguous()), _f32(table), _p(w), w.numel(), _p(x), rows, W, table.shape[0],
+                                        float(eps), _stream()), "lia_embed_rmsnorm")
+    count_launches()
+    return x
+
+
+def rms_add_norm(x, y, w_post, w_pre, h, eps):
+    """x += w_post * y / rms(y) (when y is given), then h = w_pre * x / rms(x) (when h is given); x is the fp32 residual
+    stream, updated in place."""
+    _req(x, "x", F32)
+    rows, W = x.shape
+    for t, n in ((y, "y"), (h, "h")):
+        if t is not None and not (t.is_cuda and t.is_contiguous() and tuple(t.shape) == (rows, W)):
+            raise _lib.LiaError(f"rms_add_norm: {n} must be a contiguous CUDA [{rows}, {W}] tensor")
+    check(_lib.load().lia_rms_add_norm(_p(x), _p(y), _f32(y) if y is not None else 0, _p(w_post), w_post.numel() if w_post is not None else 0,
+                                       _p(w_pre), w_pre.numel() if w_pre is not None else 0, _p(h), _f32(h) if h is not None else 0,
+                                       rows, W, float(eps), _stream()), "lia_rms_add_norm")
+    count_launches()
+    return x
+
+
+def rms_gather(x, rows, w, h, eps):
+    """h[r] = w * x[rows[r]] / rms(x[rows[r]]): the final norm of the rows whose logits are wanted."""
+    _req(x, "x", F32); _req(rows, "rows", torch.int32); _req(w, "w", F32)
+    n, W = h.shape
+    if rows.numel() != n or x.shape[1] != W or not h.is_contiguous():
+        raise _lib.LiaError("rms_gather: shapes do not agree")
+    check(_lib.load().lia_rms_gather(_p(x), _p(rows), _p(w), w.numel(), _p(h), _f32(h), n, W, float(eps), _stream()), "lia_rms_gather")
+    count_launches()
+    return h
+
+
+def clamped_glu(gate_up, up_off, F, out, limit, alpha):
+    """out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    ld = _rowmajor(gate_up, "gate_up")
+    M = gate_up.shape[0]
+    if tuple(out.shape) != (M, F) or not out.is_contiguous() or out.dtype != gate_up.dtype:
+        raise _lib.LiaError("clamped_glu: out must be a contiguous [M, F] tensor of the input's dtype")
+    check(_lib.load().lia_clamped_glu(_p(gate_up), ld, up_off, _p(out), _f32(out), M, F, float(limit), float(alpha), _stream()),
+          "lia_clamped_glu")
+    count_launches()
+    return out
+
+
+GATE_NONE, GATE_LOG_INPUT_FORGET, GATE_SIGMOID = 0, 1, 2
+
+
+def linear_small(a, w, bias, out, mode=GATE_NONE, cap=1.0):
+    """out = act(a @ w.T + bias) for a handful of outputs (per-head gates), fp32 out."""
+    lda = _rowmajor(a, "a")
+    _dev(w, "w"); _req(out, "out", F32)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or tuple(out.shape) != (M, N):
+        raise _lib.LiaError(f"linear_small: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _req(bias, "bias", F32)
+    check(_lib.load().lia_linear_small(_p(a), _f32(a), lda, _p(w), _f32(w), _p(bias), _p(out), M, N, K, mode, float(cap), _stream()),
+          "lia_linear_small")
+    count_launches()
+    return out
+
+
+def linear_plain(a, w, out, scale=1.0, batch=1, a_batch_stride=0, w_batch_stride=0, out_batch_stride=0, n=None, k=None):
+    """out[b] = scale * a[b] @ w[b].T on the CUDA cores with fp32 products and sums.  ``a`` / ``out`` are row-major 2-D
+    views (row stride free); batches are taken at element strides from their first element; ``n``, ``k`` give the
+    per-batch problem when the views are wider than one batch."""
+    lda, ldc = _rowmajor(a, "a"), _rowmajor(out, "out")
+    _dev(w, "w")
+    M = a.shape[0]
+    K = k if k is not None else a.shape[1]
+    N = n if n is not None else out.shape[1]
+    ldw = w.stride(-2) if w.dim() >= 2 else K
+    if out.shape[0] != M:
+        raise _lib.LiaError("linear_plain: a and out differ in rows")
+    check(_lib.load().lia_linear_plain(_p(a), _f32(a), lda, a_batch_stride, _p(w), _f32(w), ldw, w_batch_stride, _p(out), _f32(out), ldc,
+                                       out_batch_stride, M, N, K, batch, float(scale), _stream()), "lia_linear_plain")
+    count_launches()
+    return out
+
+
+def argmax_f32(logits, suppress_id=-1, out=None):
+    """Greedy pick over fp32 logits (lowest index on ties)."""
+    _req(logits, "logits", F32)
+    B, V = logits.shape
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    check(_lib.load().lia_argmax_f32(_p(logits), _p(_req(out, "out", torch.int64)), B, V, suppress_id, _stream()), "lia_argmax_f32")
+    count_launches()
+    return out
+
+
+def mlstm_scan(q, k, v, gates, state_S, state_n, state_m, segs, H, dim, vdim, q_scale, den_eps, o):
+    """Matrix-memory recurrence over every portion of the step (csrc/mlstm.cu).  q, k, v: column slices of one projection
+    output (same row stride); gates [rows, 2H] fp32 (log input, log forget); state tensors indexed by slot."""
+    ld = _rowmajor(q, "q")
+    if _rowmajor(k, "k") != ld or _rowmajor(v, "v") != ld or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise _lib.LiaError("mlstm_scan: q, k, v must be slices of one buffer")
+    _req(gates, "gates", F32); _req(state_S, "state_S", F32); _req(state_n, "state_n", F32); _req(state_m, "state_m", F32)
+    _req(segs, "segs", torch.int32); _req(o, "o", F32)
+    M = q.shape[0]
+    if tuple(gates.shape) != (M, 2 * H) or tuple(o.shape) != (M, H * vdim) or tuple(state_S.shape[1:]) != (H, vdim, dim):
+        raise _lib.LiaError("mlstm_scan: shapes do not agree")
+    check(_lib.load().lia_mlstm_scan(_p(q), _p(k), _p(v), _f32(q), ld, _p(gates), _p(state_S), _p(state_n), _p(state_m), _p(segs),
+                                     segs.shape[0], H, dim, vdim, float(q_scale), float(den_eps), _p(o), _stream()), "lia_mlstm_scan")
+    count_launches()
+    return o
+
+
+def headnorm_gate(o, w, gate, out, H, vdim, eps):
+    """out = o / rms_per_head(o) * w * sigmoid(gate)."""
+    _req(o, "o", F32); _req(w, "w", F32)
+    ldg = _rowmajor(gate, "gate")
+    M = o.shape[0]
+    if not out.is_contiguous() or tuple(out.shape) != (M, H * vdim) or out.dtype != gate.dtype:
+        raise _lib.LiaError("headnorm_gate: out must be a contiguous [M, H*vdim] tensor of the gate's dtype")
+    check(_lib.load().lia_headnorm_gate(_p(o), _p(w), _p(gate), ldg, _p(out), _f32(out), M, H, vdim, float(eps), _stream()),
+          "lia_headnorm_gate")
+    count_launches()
+    return out
+
+
+def latent_prep(q, dkv, c_norm_w, inv_freq, meta, cache, qa, H, dim, rot, rot_dims, kv_rank, eps):
+    """Normalised latent + rotated shared key part into ``cache[slot, pos]``; rotated query parts into ``qa[..., kv_rank:]``."""
+    ldq, ldd = _rowmajor(q, "q"), _rowmajor(dkv, "dkv")
+    _req(c_norm_w, "c_norm_w", F32); _req(inv_freq, "inv_freq", F32); _req(meta, "meta", torch.int32); _req(qa, "qa", F32)
+    M = q.shape[0]
+    if cache.dtype != q.dtype or dkv.dtype != q.dtype or not cache.is_contiguous() or cache.shape[2] != kv_rank + rot:
+        raise _lib.LiaError("latent_prep: cache must be a contiguous [slots, capacity, kv_rank + rot] tensor of the activations' dtype")
+    check(_lib.load().lia_latent_prep(_p(q), ldq, _p(dkv), ldd, _f32(q), _p(c_norm_w), _p(inv_freq), _p(meta), _p(cache), cache.stride(0),
+                                      _p(qa), M, H, dim, rot, rot_dims, kv_rank, float(eps), _stream()), "lia_latent_prep")
+    count_launches()
+
+
+def latent_attn(qa, cache, meta, gate, out, H, kv_rank, rot, scale):
+    """Causal softmax attention of every row over its sequence's cached latent rows (csrc/latent_attn.cu)."""
+    _req(qa, "qa", F32); _req(meta, "meta", torch.int32); _req(out, "out", F32)
+    if gate is not None:
+        _req(gate, "gate", F32)
+    M = qa.shape[0]
+    check(_lib.load().lia_latent_attn(_p(qa), _p(cache), _f32(cache), cache.stride(0), _p(meta), _p(gate), _p(out), M, H, kv_rank, rot,
+                                      float(scale), _stream()), "lia_latent_attn")
+    count_launches()
+    return out
