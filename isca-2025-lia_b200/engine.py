@@ -31,9 +31,11 @@ class Engine:
         n_ids, n_seg, n_meta, n_want = len(ids), len(segs) * 4, len(meta) * 2, len(want)
         words = 2 * n_ids + n_seg + n_meta + n_want
         if self._host is None or self._host.numel() < words:
-            self._host = torch.empty(max(2 * words, 1024), dtype=torch.int32).pin_memory()
-            self._copied = torch.cuda.Event()
-        else:
+            self._host = torch.empty(max(2 * words, 1024), dtype=torch.int32)
+            if self.device.type == "cuda":
+                self._host = self._host.pin_memory()
+                self._copied = torch.cuda.Event()
+        elif self._copied is not None:
             self._copied.synchronize()                     # the previous pass's copy has left the staging buffer
         host = self._host[:max(words, 2)]
         a = host.numpy()
@@ -44,7 +46,10 @@ class Engine:
         if n_want:
             a[o + n_seg + n_meta:words] = np.asarray(want, dtype=np.int32)
         dev = host.to(self.device, non_blocking=True)
-        self._copied.record()
+        if self._copied is not None:
+            self._copied.record()
+        elif dev.data_ptr() == host.data_ptr():
+            dev = dev.clone()                              # host-resident models (tests): do not alias the staging buffer
         d_ids = dev[:2 * n_ids].view(torch.int64)
         d_segs = dev[o:o + n_seg].view(-1, 4)
         d_meta = dev[o + n_seg:o + n_seg + n_meta].view(-1, 2)
