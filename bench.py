@@ -59,6 +59,9 @@ def parse():
     ap.add_argument("--weights", default=None, choices=["normal", "dummy"],
                     help="normal(0, 0.02) init (lia/modeling_opt.py:895-904) or the reference's dummy U[0,1) weights "
                          "(utils/opt-weight-gen.py:61-62; BASELINE.json configs[4])")
+    ap.add_argument("--compare-davasun", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput and per-kernel roofline fractions of "
+                         "Davasun beside OPT at equal width and depth (1 GPU, random weights); prints one JSON object")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
@@ -391,6 +394,11 @@ def _main(args, json_out):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     import lia_b200
+    if args.compare_davasun:
+        from lia_b200 import bench_compare
+        if rank == 0:
+            json_out.write(json.dumps(bench_compare.run(peaks())) + "\n")
+        return 0
     from lia_b200.modeling_opt import get_config
     cfg = get_config(args.model)
     if args.layers:

@@ -1,0 +1,209 @@
+"""`bench.py --compare-davasun`: prefill and decode throughput of Davasun at layer sizes of a real model (random weights)
+beside OPT -- the closest existing model -- at equal width and depth, with every kernel's time against its roofline.
+
+Each operation of ``ops`` is wrapped for the duration of an instrumented pass: CUDA events around the call, and the
+operation's algorithmic FLOPs and bytes from its arguments.  roofline time = max(FLOPs / peak, bytes / HBM bandwidth)
+with the measured cuBLAS bf16 peak for tensor-core GEMMs, the nominal fp32 FMA rate of the CUDA cores (SMs x 128 lanes x
+2 x max SM clock) for the kernels whose arithmetic must be fp32, and the measured copy bandwidth.  The throughput numbers
+come from separate, uninstrumented passes (>= 3 warm-ups; weights + state exceed L2).
+"""
+import time
+
+import torch
+
+from . import ops
+
+BF16 = torch.bfloat16
+
+
+def _nbytes(*ts):
+    return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+
+def _cost(name, a, kw):
+    """(flops, bytes, kind) of one call; kind: 'tc' tensor-core GEMM, 'f32' CUDA-core fp32 arithmetic, 'mem' memory-bound."""
+    if name == "gemm":
+        x, w = a[0], a[1]
+        M, K, N = x.shape[0], x.shape[1], w.shape[0]
+        return 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N), "tc"
+    if name == "linear_plain":
+        x, w, out = a[0], a[1], a[2]
+        b = kw.get("batch", 1)
+        K = kw.get("k") or x.shape[1]
+        N = kw.get("n") or out.shape[1]
+        M = x.shape[0]
+        return 2.0 * b * M * N * K, M * b * K * x.element_size() + _nbytes(w) + M * b * N * out.element_size(), "f32"
+    if name == "linear_small":
+        x, w, out = a[0], a[1], a[3]
+        return 2.0 * x.shape[0] * w.shape[0] * w.shape[1], _nbytes(x, w, out), "mem"
+    if name == "mlstm_scan":
+        q, S, segs, H, dim, vdim, o = a[0], a[4], a[7], a[8], a[9], a[10], a[13]
+        M = q.shape[0]
+        state = 2.0 * segs.shape[0] * H * dim * vdim * 4
+        return 4.0 * M * H * dim * vdim, state + M * H * (2 * dim + vdim) * q.element_size() + _nbytes(o), "f32"
+    if name == "latent_attn":
+        qa, cache, meta, out, H, rank, rot = a[0], a[1], a[2], a[4], a[5], a[6], a[7]
+        keys = float(kw.get("_keys", 0))                                           # sum over rows of visible keys
+        return 2.0 * keys * H * (2 * rank + rot), _nbytes(qa, out) + kw.get("_ctx", 0) * (rank + rot) * cache.element_size(), "f32"
+    if name == "attn_prefill":
+        q, kc, B, S = a[0], a[1], a[3], a[4]
+        H, d = kc.shape[2], kc.shape[3]
+        return 2.0 * B * H * S * S * d, 4.0 * B * S * H * d * 2, "tc"            # causal: half of 4 B H S^2 d
+    if name == "attn_decode":
+        q, kc, B, T = a[0], a[1], a[3], a[4]
+        H, d = kc.shape[2], kc.shape[3]
+        return 4.0 * B * H * T * d, 4.0 * B * T * H * d, "mem"
+    ts = [t for t in list(a) + list(kw.values()) if isinstance(t, torch.Tensor) and t.is_cuda]
+    return 0.0, float(_nbytes(*ts)), "mem"
+
+
+class Instrument:
+    NAMES = ("gemm", "linear_plain", "linear_small", "mlstm_scan", "headnorm_gate", "latent_prep", "latent_attn", "clamped_glu",
+             "rms_add_norm", "embed_rmsnorm", "rms_gather", "layernorm", "attn_prefill", "attn_decode", "embed", "argmax", "argmax_f32")
+
+    def __init__(self):
+        self.records, self.saved, self.extra = [], {}, {}
+
+    def __enter__(self):
+        for n in self.NAMES:
+            fn = getattr(ops, n)
+            self.saved[n] = fn
+
+            def wrapped(*a, _n=n, _fn=fn, **kw):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = _fn(*a, **kw)
+                e1.record()
+                self.records.append((_n, e0, e1, _cost(_n, a, dict(kw, **self.extra))))
+                return r
+            setattr(ops, n, wrapped)
+        return self
+
+    def __exit__(self, *exc):
+        for n, fn in self.saved.items():
+            setattr(ops, n, fn)
+
+    def table(self, pk):
+        torch.cuda.synchronize()
+        agg = {}
+        for n, e0, e1, (fl, by, kind) in self.records:
+            peak = pk["bf16_burst"] * 1e12 if kind == "tc" else pk["fp32_nominal_tflops"] * 1e12
+            ideal = max(fl / peak if kind != "mem" else 0.0, by / (pk["hbm_gbs"] * 1e9))
+            r = agg.setdefault(n, {"calls": 0, "ms": 0.0, "roofline_ms": 0.0, "gflop": 0.0, "mb": 0.0, "bound": kind})
+            r["calls"] += 1
+            r["ms"] += e0.elapsed_time(e1)
+            r["roofline_ms"] += ideal * 1e3
+            r["gflop"] += fl / 1e9
+            r["mb"] += by / 1e6
+        for r in agg.values():
+            r["of_roofline"] = round(r["roofline_ms"] / r["ms"], 4) if r["ms"] > 0 else None
+            for k in ("ms", "roofline_ms", "gflop", "mb"):
+                r[k] = round(r[k], 4)
+        return agg
+
+
+def davasun_config(width, n_layers):
+    """Layer sizes of a ~1-3 B model: mLSTM heads of 256 x 512, latent attention with 128 + 64 query/key channels and a
+    512-wide latent, a 2.75 x feed-forward on the attention layers; one attention layer in every four."""
+    H = max(1, width // 512)
+    ml = {"type": "mlstm", "mixer": {"heads": H, "dim": 256, "vdim": 512, "gate_cap": 15.0}, "mlp": None}
+    la = {"type": "latent_attention",
+          "mixer": {"heads": width // 128, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "rot": {"base": 10000.0, "dims": 64},
+                    "scale": 192 ** -0.5},
+          "mlp": {"kind": "dense", "ff": width * 11 // 4, "limit": 7.0}}
+    layers = [la if i % 4 == 1 else ml for i in range(n_layers)]
+    return {"architecture": "Davasun", "vocab": 32000, "width": width, "layers": layers, "loop": {"start": 0, "stop": 0, "times": 1},
+            "norm": {"eps": 1e-6}, "logit_scale": 1.0}
+
+
+def _timed(fn, warmup=3, iters=5):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=2048, decode_batches=(1, 16), new=16):
+    from .engine import Engine
+    from .modeling_davasun import DavasunConfig, DavasunForCausalLM
+    from .modeling_opt import OPTConfig, OPTForCausalLM
+    dev = torch.device("cuda", 0)
+    props = torch.cuda.get_device_properties(dev)
+    pk = dict(pk, fp32_nominal_tflops=props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12)
+    out = {"peaks": pk, "sizes": []}
+    g = torch.Generator().manual_seed(0)
+    for width in widths:
+        rec = {"width": width, "layers": n_layers, "prompt": prompt, "decode_context": decode_ctx}
+        # ---------------- Davasun
+        cfg = DavasunConfig.from_dict(davasun_config(width, n_layers))
+        m = DavasunForCausalLM(cfg, dev, BF16).init_weights(seed=1)
+        toks = torch.randint(0, cfg.vocab, (prompt,), generator=g).tolist()
+        eng = Engine(m, max_tokens=decode_ctx + new + 8, max_requests=max(decode_batches), max_rows=prompt)
+
+        def prefill():
+            eng.step([{"id": "p", "tokens": toks, "want": [prompt - 1]}], end=["p"])
+        ms = _timed(prefill)
+        d = {"prefill_ms": round(ms, 3), "prefill_tokens_per_s": round(prompt / ms * 1e3, 1)}
+        with Instrument() as ins:
+            ins.extra = {"_keys": prompt * (prompt + 1) / 2, "_ctx": prompt}
+            prefill()
+        d["prefill_kernels"] = ins.table(pk)
+        for B in decode_batches:
+            ids = list(range(B))
+            ctx = torch.randint(0, cfg.vocab, (decode_ctx,), generator=g).tolist()
+            for i in ids:
+                eng.step([{"id": i, "tokens": ctx, "want": []}])
+            step = lambda: eng.step([{"id": i, "tokens": [7], "want": [0]} for i in ids])  # noqa: E731
+            ms = _timed(step, warmup=3, iters=new - 4)
+            d[f"decode_b{B}_ms_per_step"] = round(ms, 3)
+            d[f"decode_b{B}_tokens_per_s"] = round(B / ms * 1e3, 1)
+            with Instrument() as ins:
+                ins.extra = {"_keys": B * (decode_ctx + new), "_ctx": B * (decode_ctx + new)}
+                step()
+            d[f"decode_b{B}_kernels"] = ins.table(pk)
+            eng.step([], end=ids)
+        rec["davasun"] = d
+        del eng, m
+        torch.cuda.empty_cache()
+        # ---------------- OPT at equal width and depth (head_dim 128, 4x feed-forward)
+        ocfg = OPTConfig(hidden_size=width, num_hidden_layers=n_layers, num_attention_heads=width // 128, ffn_dim=4 * width,
+                         vocab_size=32000, max_position_embeddings=prompt + decode_ctx + new + 8, name=f"opt-w{width}")
+        om = OPTForCausalLM(ocfg, dev).init_weights(seed=1)
+        o = {}
+        ids1 = torch.randint(3, 32000, (1, prompt), generator=g).to(dev)
+        gen = lambda x, n: om.generate(x, max_new_tokens=n, min_new_tokens=n, prefill_policy=0, decoding_policy=0)  # noqa: E731
+        _timed(lambda: gen(ids1, 1), warmup=3, iters=1)
+        ms = om.last_timing["prefill_s"] * 1e3
+        o["prefill_ms"] = round(ms, 3)
+        o["prefill_tokens_per_s"] = round(prompt / ms * 1e3, 1)
+        om.use_cuda_graphs = False
+        with Instrument() as ins:
+            gen(ids1, 1)
+        o["prefill_kernels"] = ins.table(pk)
+        for B in decode_batches:
+            idsb = torch.randint(3, 32000, (B, decode_ctx), generator=g).to(dev)
+            om.use_cuda_graphs = True
+            _timed(lambda: gen(idsb, new), warmup=3, iters=1)
+            dec = om.last_timing["decode_s"]
+            ms = sum(dec) / len(dec) * 1e3
+            o[f"decode_b{B}_ms_per_step"] = round(ms, 3)
+            o[f"decode_b{B}_tokens_per_s"] = round(B / ms * 1e3, 1)
+            om.use_cuda_graphs = False
+            before = None
+            with Instrument() as ins:
+                gen(idsb, 2)
+            # keep the records of the decode step only (after the prefill's): the last layer loop + head
+            per_step = len(ins.records) - next(i for i, r in enumerate(ins.records) if r[0] == "attn_decode") + 2
+            ins.records = ins.records[-per_step:]
+            o[f"decode_b{B}_kernels"] = ins.table(pk)
+        rec["opt"] = o
+        del om
+        torch.cuda.empty_cache()
+        out["sizes"].append(rec)
+    return out

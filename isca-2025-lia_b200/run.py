@@ -95,9 +95,41 @@ def build_inputs(args, vocab_size, tokenizer=None, search_dirs=()):
     return row.expand(args.batch_size, row.shape[1]).contiguous().to(torch.int64), text
 
 
+def run_step_model(args, cls):
+    """A checkpoint whose class is served by the step engine (registry.model_class(...).step_serving): greedy generation of
+    --batch-size prompts of --input-tokens synthetic ids, --num-iter times, with the reference's summary lines
+    (run_generation.py:330-354).  The placement flags of the OPT path do not apply (everything is resident on the GPU)."""
+    import torch
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    model = cls.from_pretrained(args.model_id, device=dev, dtype=torch.float32 if args.dtype == "float32" else torch.bfloat16)
+    input_ids, _ = build_inputs(args, model.config.vocab)
+    total, timed = 0.0, 0
+    for i in range(args.num_iter):
+        tic = time.time()
+        out = model.generate(input_ids, max_new_tokens=args.max_new_tokens)
+        toc = time.time()
+        print([int(o.shape[0]) - input_ids.shape[1] for o in out][:4], flush=True)
+        print("Iteration: %d, Time: %.6f sec" % (i, toc - tic), flush=True)
+        if i >= args.num_warmup:
+            total, timed = total + toc - tic, timed + 1
+    latency = total / max(1, timed)
+    print("\n", "-" * 10, "Summary:", "-" * 10)
+    print("Inference latency: %.3f sec." % latency)
+    print("Throughput: %.1f tokens/sec (batch %d x %d new tokens)" % (args.batch_size * args.max_new_tokens / max(latency, 1e-9),
+                                                                     args.batch_size, args.max_new_tokens))
+    return 0
+
+
 def main(argv=None):
     args = build_parser().parse_args(argv)
     print(args)
+    if os.path.isdir(args.model_id):
+        import lia_b200  # noqa: F401
+        from lia_b200 import registry
+        cls = registry.model_class(args.model_id)          # config.json names the design
+        if getattr(cls, "step_serving", False):
+            return run_step_model(args, cls)
     if args.dtype != "bfloat16":
         print("error: only --dtype bfloat16 is implemented on the B200 path", file=sys.stderr)
         return 2
