@@ -295,9 +295,11 @@ int lia_latent_prep(const void* q, int ldq, const void* dkv, int ldd, int act_f3
                     const int* meta, void* cache, long long slot_stride, float* qa, int M, int H, int dim, int rot, int rot_dims,
                     int kv_rank, float eps, lia_stream_t stream);
 /* out[row][h] = gate[row][h] * sum_{s <= pos(row)} softmax_s((qa[row][h] . cache[slot][s]) * scale) cache[slot][s][:kv_rank]
- * (gate may be NULL: no output gate) */
+ * (gate may be NULL: no output gate).  nsplit > 1 splits every row's keys over nsplit blocks (decoding over a long history);
+ * it needs a workspace of lia_latent_attn_workspace_floats(...) floats and runs a second, combining kernel. */
+size_t lia_latent_attn_workspace_floats(int M, int H, int kv_rank, int nsplit);
 int lia_latent_attn(const float* qa, const void* cache, int cache_f32, long long slot_stride, const int* meta, const float* gate,
-                    float* out, int M, int H, int kv_rank, int rot, float scale, lia_stream_t stream);
+                    float* out, float* workspace, int nsplit, int M, int H, int kv_rank, int rot, float scale, lia_stream_t stream);
 
 #ifdef __cplusplus
 }

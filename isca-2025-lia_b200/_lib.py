@@ -99,7 +99,8 @@ _PROTOTYPES = {
     "lia_headnorm_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
     "lia_latent_prep": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
-    "lia_latent_attn": (c_int, [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_latent_attn_workspace_floats": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "lia_latent_attn": (c_int, [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
 }
 
 EXPORTS = tuple(_PROTOTYPES)

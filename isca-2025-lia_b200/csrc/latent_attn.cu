@@ -9,8 +9,9 @@
 //   latent_prep:  RMS-norm of the latent part with its per-channel weight, rotary embedding ("rotate half": channel i is
 //                 paired with i + dims/2) of the shared key part at the token's position, both written into the cache row;
 //                 the same rotation of each head's rotated query part, written behind that head's q~ slot.
-//   latent_attn:  one block per (token, group of up to 8 heads); 32 cached rows at a time are staged in shared memory as
-//                 fp32, scored by all heads of the group, folded into a running softmax, and accumulated.
+//   latent_attn:  one block per (token, group of up to 8 heads, range of keys); 32 cached rows at a time are staged in shared
+//                 memory as fp32, scored (warp = head, lane = key), folded into a running softmax, and accumulated.  Few rows
+//                 and a long history (decoding): the keys are split over several blocks and a second kernel combines.
 #include <math.h>
 
 #include "common.cuh"
@@ -70,30 +71,53 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const T* __restrict__ 
   }
 }
 
-constexpr int TK = 32;     // cached rows per stage (= one warp's lanes in the softmax step)
-constexpr int HG = 8;      // heads per block (= warps per block)
+constexpr int TK = 32;     // cached rows per stage (= one warp's lanes: lane j scores key j)
+constexpr int HG = 8;      // heads per block (= warps per block: warp w scores head w)
 
-// qa [M][H][D] fp32, cache [slot][capacity][D], out [M][H][kv_rank] fp32, times gate[M][H] (a per-head output gate) if given.  RM = ceil(kv_rank / 256).
+__host__ __device__ inline int padded_row(int D) { return (D + 3) / 4 * 4 + 4; }   // smem row stride: 16-byte rows, conflict-free 128-bit reads
+
+// one cached row segment of VEC numbers as floats (128-bit load)
+__device__ __forceinline__ void load_vec(const bf16* p, float* f) { unpack8(*reinterpret_cast<const uint4*>(p), f); }
+__device__ __forceinline__ void load_vec(const float* p, float* f) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <typename T> struct Vec { static constexpr int N = 8; };
+template <> struct Vec<float> { static constexpr int N = 4; };
+
+// qa [M][H][D] fp32, cache [slot][capacity][D], out [M][H][kv_rank] fp32, times gate[M][H] (a per-head output gate) if
+// given.  RM = ceil(kv_rank / 256).  gridDim.z = nsplit: block z takes the z-th part of the row's keys; with nsplit > 1 the
+// unnormalised sums go to `part` ([M][H][nsplit][kv_rank]) and (max, sum) to `part_ml`, and latent_combine_kernel finishes.
 template <typename T, int RM>
 __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ cache, long long slot_stride,
-                                                          const int* __restrict__ meta, const float* __restrict__ gate, float* __restrict__ out, int H,
-                                                          int kv_rank, int rot, float scale) {
-  extern __shared__ float sm[];
-  const int D = kv_rank + rot;
-  float* qs = sm;                    // [HG][D]
-  float* ks = qs + HG * D;           // [TK][D]
-  float* ps = ks + TK * D;           // [HG][TK]
+                                                          const int* __restrict__ meta, const float* __restrict__ gate, float* __restrict__ out,
+                                                          float* __restrict__ part, float2* __restrict__ part_ml, int H, int kv_rank, int rot,
+                                                          float scale) {
+  extern __shared__ __align__(16) float sm[];
+  const int D = kv_rank + rot, DS = padded_row(D), G4 = (DS - 4) / 4;
+  float* qs = sm;                    // [HG][DS]
+  float* ks = qs + HG * DS;          // [TK][DS]
+  float* ps = ks + TK * DS;          // [HG][TK]
   float* alpha = ps + HG * TK;       // [HG]
   float* lsum = alpha + HG;          // [HG]
-  const int row = blockIdx.x, h0 = blockIdx.y * HG;
+  float* msum = lsum + HG;           // [HG]
+  const int row = blockIdx.x, h0 = blockIdx.y * HG, z = blockIdx.z, nsplit = gridDim.z;
   const int nh = min(HG, H - h0);
   const int slot = meta[2 * row], pos = meta[2 * row + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* crows = cache + (size_t)slot * slot_stride;
+  const int tiles = (pos + TK) / TK, per = (tiles + nsplit - 1) / nsplit;
+  const int j_begin = z * per * TK, j_end = min(pos + 1, (z + 1) * per * TK);
+  constexpr int VEC = Vec<T>::N;
+  const bool vec = (D % VEC == 0) && (slot_stride % VEC == 0) && (reinterpret_cast<uintptr_t>(cache) % 16 == 0);
 
-  for (int e = threadIdx.x; e < HG * D; e += 256) {
-    const int hh = e / D;
-    qs[e] = hh < nh ? qa[((size_t)row * H + h0) * D + e] : 0.f;
+  for (int e = threadIdx.x; e < HG * DS; e += 256) {
+    const int hh = e / DS, d = e - hh * DS;
+    qs[e] = (hh < nh && d < D) ? qa[((size_t)row * H + h0 + hh) * D + d] : 0.f;
+  }
+  for (int e = threadIdx.x; e < TK * (DS - D); e += 256) {          // the pad columns of the key stage stay zero
+    const int j = e / (DS - D);
+    ks[j * DS + D + (e - j * (DS - D))] = 0.f;
   }
   float acc[HG][RM];
 #pragma unroll
@@ -102,26 +126,41 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
     for (int i = 0; i < RM; ++i) acc[hh][i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;          // of head `warp`, identical in all its lanes
 
-  for (int j0 = 0; j0 <= pos; j0 += TK) {
+  for (int j0 = j_begin; j0 < j_end; j0 += TK) {
     __syncthreads();                             // previous stage fully consumed (and qs written, first time)
-    const int nk = min(TK, pos + 1 - j0);
-    for (int e = threadIdx.x; e < TK * D; e += 256) {
-      const int j = e / D;
-      ks[e] = j < nk ? ldf(crows + (size_t)j0 * D + e) : 0.f;
+    const int nk = min(TK, j_end - j0);
+    if (vec) {
+      const int per_row = D / VEC;
+      for (int e = threadIdx.x; e < TK * per_row; e += 256) {
+        const int j = e / per_row, c = (e - j * per_row) * VEC;
+        float f[VEC];
+        if (j < nk) {
+          load_vec(crows + (size_t)(j0 + j) * D + c, f);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) f[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4*>(ks + j * DS + c + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+      }
+    } else {
+      for (int e = threadIdx.x; e < TK * D; e += 256) {
+        const int j = e / D, d = e - j * D;
+        ks[j * DS + d] = j < nk ? ldf(crows + (size_t)(j0 + j) * D + d) : 0.f;
+      }
     }
     __syncthreads();
-    for (int p = warp; p < nh * TK; p += 8) {
-      const int hh = p / TK, j = p - hh * TK;
-      float dot = 0.f;
-      for (int d = lane; d < D; d += 32) dot = fmaf(qs[hh * D + d], ks[j * D + d], dot);
-      dot = warp_sum(dot);
-      if (lane == 0) ps[p] = j < nk ? dot * scale : -INFINITY;
-    }
-    __syncthreads();
-    if (warp < nh) {
-      const float s = ps[warp * TK + lane];
-      const float m_new = fmaxf(m_run, warp_max(s));          // finite: the stage holds at least one visible key
-      const float pr = expf(s - m_new);
+    if (warp < nh) {                             // warp = head, lane = key: a full dot product per lane, then the running softmax
+      const float4* q4 = reinterpret_cast<const float4*>(qs + warp * DS);
+      const float4* k4 = reinterpret_cast<const float4*>(ks + lane * DS);
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      for (int g = 0; g < G4; ++g) {
+        const float4 a = q4[g], b = k4[g];
+        d0 = fmaf(a.x, b.x, d0); d1 = fmaf(a.y, b.y, d1); d2 = fmaf(a.z, b.z, d2); d3 = fmaf(a.w, b.w, d3);
+      }
+      const float sc = lane < nk ? ((d0 + d1) + (d2 + d3)) * scale : -INFINITY;
+      const float m_new = fmaxf(m_run, warp_max(sc));          // finite: the stage holds at least one visible key
+      const float pr = expf(sc - m_new);
       const float a = expf(m_run - m_new);
       l_run = l_run * a + warp_sum(pr);
       m_run = m_new;
@@ -135,55 +174,101 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
 #pragma unroll
       for (int i = 0; i < RM; ++i) acc[hh][i] *= a;
     }
-    for (int j = 0; j < nk; ++j) {
-      float kv[RM];
+    // four keys at a time: weights of absent keys are 0 and their staged rows are zero, so the last group may overrun nk
+    for (int j = 0; j < nk; j += 4) {
+      float kv[4][RM];
 #pragma unroll
-      for (int i = 0; i < RM; ++i) {
-        const int r = threadIdx.x + 256 * i;
-        kv[i] = r < kv_rank ? ks[j * D + r] : 0.f;
-      }
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int i = 0; i < RM; ++i) {
+          const int r = threadIdx.x + 256 * i;
+          kv[u][i] = r < kv_rank ? ks[(j + u) * DS + r] : 0.f;
+        }
 #pragma unroll
       for (int hh = 0; hh < HG; ++hh) {
-        const float pw = ps[hh * TK + j];                       // rows of absent heads hold stale values: never stored
+        if (hh < nh) {
+          const float4 pw = *reinterpret_cast<const float4*>(ps + hh * TK + j);
 #pragma unroll
-        for (int i = 0; i < RM; ++i) acc[hh][i] = fmaf(pw, kv[i], acc[hh][i]);
+          for (int i = 0; i < RM; ++i) {
+            acc[hh][i] = fmaf(pw.x, kv[0][i], acc[hh][i]);
+            acc[hh][i] = fmaf(pw.y, kv[1][i], acc[hh][i]);
+            acc[hh][i] = fmaf(pw.z, kv[2][i], acc[hh][i]);
+            acc[hh][i] = fmaf(pw.w, kv[3][i], acc[hh][i]);
+          }
+        }
       }
     }
   }
-  if (warp < nh && lane == 0) lsum[warp] = l_run;
+  if (warp < nh && lane == 0) {
+    lsum[warp] = l_run;
+    msum[warp] = m_run;
+  }
   __syncthreads();
 #pragma unroll
   for (int hh = 0; hh < HG; ++hh) {
     if (hh < nh) {
-      const float invl = (gate ? gate[(size_t)row * H + h0 + hh] : 1.0f) / lsum[hh];
+      const size_t rh = (size_t)row * H + h0 + hh;
+      if (nsplit == 1) {
+        const float invl = (gate ? gate[rh] : 1.0f) / lsum[hh];
 #pragma unroll
-      for (int i = 0; i < RM; ++i) {
-        const int r = threadIdx.x + 256 * i;
-        if (r < kv_rank) out[((size_t)row * H + h0 + hh) * kv_rank + r] = acc[hh][i] * invl;
+        for (int i = 0; i < RM; ++i) {
+          const int r = threadIdx.x + 256 * i;
+          if (r < kv_rank) out[rh * kv_rank + r] = acc[hh][i] * invl;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < RM; ++i) {
+          const int r = threadIdx.x + 256 * i;
+          if (r < kv_rank) part[(rh * nsplit + z) * kv_rank + r] = acc[hh][i];
+        }
+        if (threadIdx.x == 0) part_ml[rh * nsplit + z] = make_float2(msum[hh], lsum[hh]);
       }
     }
   }
 }
 
+// out[rh] = gate * sum_z part[rh][z] e^(m_z - m) / sum_z l_z e^(m_z - m), m = max_z m_z (a part without keys has m = -inf, l = 0)
+__global__ void __launch_bounds__(128) latent_combine_kernel(const float* __restrict__ part, const float2* __restrict__ part_ml,
+                                                             const float* __restrict__ gate, float* __restrict__ out, int kv_rank, int nsplit) {
+  const size_t rh = blockIdx.x;
+  float m = -INFINITY;
+  for (int z = 0; z < nsplit; ++z) m = fmaxf(m, part_ml[rh * nsplit + z].x);
+  float l = 0.f;
+  for (int z = 0; z < nsplit; ++z) l += part_ml[rh * nsplit + z].y * expf(part_ml[rh * nsplit + z].x - m);
+  const float g = (gate ? gate[rh] : 1.0f) / l;
+  for (int r = threadIdx.x; r < kv_rank; r += 128) {
+    float s = 0.f;
+    for (int z = 0; z < nsplit; ++z) s = fmaf(part[(rh * nsplit + z) * kv_rank + r], expf(part_ml[rh * nsplit + z].x - m), s);
+    out[rh * kv_rank + r] = s * g;
+  }
+}
+
 template <typename T, int RM>
-int launch_attn(const float* qa, const void* cache, long long slot_stride, const int* meta, const float* gate, float* out, int M, int H, int kv_rank, int rot,
-                float scale, cudaStream_t stream) {
-  const int D = kv_rank + rot;
-  const size_t smem = ((size_t)HG * D + (size_t)TK * D + HG * TK + 2 * HG) * sizeof(float);
-  LIA_CHECK_ARG(smem <= 200 * 1024, "lia_latent_attn: a cache row of %d numbers does not fit the shared-memory stage", D);
+int launch_attn(const float* qa, const void* cache, long long slot_stride, const int* meta, const float* gate, float* out, float* ws, int nsplit,
+                int M, int H, int kv_rank, int rot, float scale, cudaStream_t stream) {
+  const int DS = padded_row(kv_rank + rot);
+  const size_t smem = ((size_t)HG * DS + (size_t)TK * DS + HG * TK + 3 * HG) * sizeof(float);
+  LIA_CHECK_ARG(smem <= 200 * 1024, "lia_latent_attn: a cache row of %d numbers does not fit the shared-memory stage", kv_rank + rot);
   if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(latent_attn_kernel<T, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(M, (H + HG - 1) / HG);
-  latent_attn_kernel<T, RM><<<grid, 256, smem, stream>>>(qa, reinterpret_cast<const T*>(cache), slot_stride, meta, gate, out, H, kv_rank, rot, scale);
+  dim3 grid(M, (H + HG - 1) / HG, nsplit);
+  float* part = ws;
+  float2* part_ml = reinterpret_cast<float2*>(ws + (size_t)M * H * nsplit * kv_rank);
+  latent_attn_kernel<T, RM><<<grid, 256, smem, stream>>>(qa, reinterpret_cast<const T*>(cache), slot_stride, meta, gate, out, part, part_ml, H,
+                                                         kv_rank, rot, scale);
   LIA_LAUNCH_CHECK();
+  if (nsplit > 1) {
+    latent_combine_kernel<<<(unsigned)((size_t)M * H), 128, 0, stream>>>(part, part_ml, gate, out, kv_rank, nsplit);
+    LIA_LAUNCH_CHECK();
+  }
   return LIA_OK;
 }
 
 template <typename T>
-int dispatch_attn(const float* qa, const void* cache, long long slot_stride, const int* meta, const float* gate, float* out, int M, int H, int kv_rank, int rot,
-                  float scale, cudaStream_t stream) {
-  if (kv_rank <= 256) return launch_attn<T, 1>(qa, cache, slot_stride, meta, gate, out, M, H, kv_rank, rot, scale, stream);
-  if (kv_rank <= 512) return launch_attn<T, 2>(qa, cache, slot_stride, meta, gate, out, M, H, kv_rank, rot, scale, stream);
-  return launch_attn<T, 4>(qa, cache, slot_stride, meta, gate, out, M, H, kv_rank, rot, scale, stream);
+int dispatch_attn(const float* qa, const void* cache, long long slot_stride, const int* meta, const float* gate, float* out, float* ws, int nsplit,
+                  int M, int H, int kv_rank, int rot, float scale, cudaStream_t stream) {
+  if (kv_rank <= 256) return launch_attn<T, 1>(qa, cache, slot_stride, meta, gate, out, ws, nsplit, M, H, kv_rank, rot, scale, stream);
+  if (kv_rank <= 512) return launch_attn<T, 2>(qa, cache, slot_stride, meta, gate, out, ws, nsplit, M, H, kv_rank, rot, scale, stream);
+  return launch_attn<T, 4>(qa, cache, slot_stride, meta, gate, out, ws, nsplit, M, H, kv_rank, rot, scale, stream);
 }
 
 }  // namespace
@@ -206,11 +291,17 @@ extern "C" int lia_latent_prep(const void* q, int ldq, const void* dkv, int ldd,
   return LIA_OK;
 }
 
+extern "C" size_t lia_latent_attn_workspace_floats(int M, int H, int kv_rank, int nsplit) {
+  if (nsplit <= 1) return 0;
+  return (size_t)M * H * nsplit * ((size_t)kv_rank + 2);
+}
+
 extern "C" int lia_latent_attn(const float* qa, const void* cache, int cache_f32, long long slot_stride, const int* meta, const float* gate,
-                               float* out, int M, int H, int kv_rank, int rot, float scale, lia_stream_t stream_) {
+                               float* out, float* workspace, int nsplit, int M, int H, int kv_rank, int rot, float scale, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(qa && cache && meta && out, "lia_latent_attn: null pointer");
   LIA_CHECK_ARG(M > 0 && H > 0 && H <= 65535 * HG && kv_rank > 0 && kv_rank <= 1024 && rot >= 0, "lia_latent_attn: bad shape M=%d H=%d kv_rank=%d rot=%d", M, H, kv_rank, rot);
-  if (cache_f32) return dispatch_attn<float>(qa, cache, slot_stride, meta, gate, out, M, H, kv_rank, rot, scale, stream);
-  return dispatch_attn<bf16>(qa, cache, slot_stride, meta, gate, out, M, H, kv_rank, rot, scale, stream);
+  LIA_CHECK_ARG(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || workspace != nullptr), "lia_latent_attn: %d key ranges need a workspace", nsplit);
+  if (cache_f32) return dispatch_attn<float>(qa, cache, slot_stride, meta, gate, out, workspace, nsplit, M, H, kv_rank, rot, scale, stream);
+  return dispatch_attn<bf16>(qa, cache, slot_stride, meta, gate, out, workspace, nsplit, M, H, kv_rank, rot, scale, stream);
 }

@@ -22,6 +22,18 @@ namespace {
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
 template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+// loads that stay where they are written: issued at the top of a stage, consumed after it (the compiler would otherwise sink
+// them to their first use and expose the whole memory latency once per stage)
+__device__ __forceinline__ float ld_early(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float ld_early(const bf16* p) {
+  unsigned short u;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(u) : "l"(p));
+  return __uint_as_float((unsigned)u << 16);
+}
 template <typename T> __device__ __forceinline__ void stf(T* p, float v);
 template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
@@ -71,14 +83,14 @@ __global__ void __launch_bounds__(NW * 32) mlstm_scan_kernel(const T* __restrict
         if (tok < len) {
           const size_t row = (size_t)(row0 + tok);
           if (j < DP) {
-            if (j < dim) val = ldf(q + row * ld + h * dim + j) * q_scale;
+            if (j < dim) val = ld_early(q + row * ld + h * dim + j);
           } else if (j < 2 * DP) {
-            if (j - DP < dim) val = ldf(k + row * ld + h * dim + (j - DP));
+            if (j - DP < dim) val = ld_early(k + row * ld + h * dim + (j - DP));
           } else if (j < 2 * DP + CB) {
             const int c = colb + j - 2 * DP;
-            if (c < vdim) val = ldf(v + row * ld + h * vdim + c);
+            if (c < vdim) val = ld_early(v + row * ld + h * vdim + c);
           } else {
-            val = gates[row * 2 * H + (j - 2 * DP - CB) * H + h];
+            val = ld_early(gates + row * 2 * H + (j - 2 * DP - CB) * H + h);
           }
         }
       }
@@ -101,23 +113,26 @@ __global__ void __launch_bounds__(NW * 32) mlstm_scan_kernel(const T* __restrict
     if (g + 1 < groups) fetch(g + 1);            // in flight while this group is processed
     const float* st = stage + (g & 1) * TB * ROWF;
     const int nt = min(TB, len - g * TB);
-    for (int t = 0; t < nt; ++t) {
+    auto token = [&](int t) {
       const float* tk = st + t * ROWF;
       const float ig = tk[2 * DP + CB], fg = tk[2 * DP + CB + 1];
       const float m_new = fmaxf(fg + m, ig);
       const float a = expf(fg + m - m_new), b = expf(ig - m_new);
+      float vc[CW];
+#pragma unroll
+      for (int c = 0; c < CW; ++c) vc[c] = tk[2 * DP + warp * CW + c];
       float part[CW + 1];
 #pragma unroll
       for (int c = 0; c <= CW; ++c) part[c] = 0.f;
 #pragma unroll
       for (int i = 0; i < DR; ++i) {
-        const float qv = tk[lane + 32 * i], kv = tk[DP + lane + 32 * i];
+        const float qv = tk[lane + 32 * i] * q_scale, kv = tk[DP + lane + 32 * i];
         const float bk = b * kv;
         n[i] = fmaf(a, n[i], bk);
         part[CW] = fmaf(n[i], qv, part[CW]);
 #pragma unroll
         for (int c = 0; c < CW; ++c) {
-          S[i][c] = fmaf(a, S[i][c], bk * tk[2 * DP + warp * CW + c]);
+          S[i][c] = fmaf(a, S[i][c], bk * vc[c]);
           part[c] = fmaf(S[i][c], qv, part[c]);
         }
       }
@@ -129,7 +144,8 @@ __global__ void __launch_bounds__(NW * 32) mlstm_scan_kernel(const T* __restrict
 #pragma unroll
       for (int c = 1; c < CW; ++c) mine = (lane == c) ? part[c] : mine;
       if (lane < CW && col0 + lane < vdim) o[(size_t)(row0 + g * TB + t) * H * vdim + h * vdim + col0 + lane] = mine / den;
-    }
+    };
+    for (int t = 0; t < nt; ++t) token(t);
     if (g + 1 < groups) put((g + 1) & 1);        // the other buffer: last read two groups ago, before the barrier below
     __syncthreads();
   }

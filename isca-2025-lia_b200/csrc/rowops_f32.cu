@@ -114,39 +114,113 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, int ld, int up_off,
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
+// 8 consecutive numbers of a row as floats; `vec` says that the 16-byte (bf16) / 32-byte (fp32) vector load is legal here
+template <typename T> __device__ __forceinline__ void load8(const T* p, int k, int K, bool vec, float* f);
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, int k, int K, bool vec, float* f) {
+  if (vec && k + 8 <= K) {
+    unpack8(*reinterpret_cast<const uint4*>(p + k), f);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = k + j < K ? __bfloat162float(p[k + j]) : 0.f;
+  }
+}
+template <> __device__ __forceinline__ void load8<float>(const float* p, int k, int K, bool vec, float* f) {
+  if (vec && k + 8 <= K) {
+    const float4 lo = *reinterpret_cast<const float4*>(p + k), hi = *reinterpret_cast<const float4*>(p + k + 4);
+    f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w; f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = k + j < K ? p[k + j] : 0.f;
+  }
+}
+template <typename T> __device__ __forceinline__ bool vec_ok(const T* p, long long ld) {
+  return (reinterpret_cast<uintptr_t>(p) % 16 == 0) && (ld * (long long)sizeof(T)) % 16 == 0;
+}
+
 // out[m][n] = act(sum_k a[m][k] w[n][k] + bias[n]) for a handful of outputs (gates: one per head), fp32 out.
 // mode 0: identity; 1: n < N/2 -> cap*tanh(z/cap), n >= N/2 -> logsigmoid(cap*tanh(z/cap)); 2: sigmoid.
-// One warp per row; 8 outputs per sweep over the row.
+// One block of 4 warps per row: the warps split k (8 numbers per lane and sweep, 128-bit loads), 8 outputs per sweep,
+// partial sums meet in shared memory in a fixed order.
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) linear_small_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, const float* __restrict__ bias,
                                                            float* __restrict__ out, int M, int N, int K, int mode, float cap) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= M) return;
+  __shared__ float part[4][8];
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TA* ar = a + (size_t)row * lda;
+  const bool va = vec_ok(a, lda), vw = vec_ok(w, K);
   for (int n0 = 0; n0 < N; n0 += 8) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float av = ldf(ar + k);
+    for (int k = threadIdx.x * 8; k < K; k += 128 * 8) {
+      float av[8], wv[8];
+      load8(ar, k, K, va, av);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (n0 + j < N) acc[j] = fmaf(av, ldf(w + (size_t)(n0 + j) * K + k), acc[j]);
+      for (int j = 0; j < 8; ++j) {
+        if (n0 + j < N) {
+          load8(w + (size_t)(n0 + j) * K, k, K, vw, wv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[j] = fmaf(av[i], wv[i], acc[j]);
+        }
+      }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float s = warp_sum(acc[j]);
-      const int n = n0 + j;
-      if (lane == 0 && n < N) {
-        float z = s + (bias ? bias[n] : 0.f);
-        if (mode == 1) {
-          z = cap * tanhf(z / cap);
-          if (n >= N / 2) z = log_sigmoid(z);
-        } else if (mode == 2) {
-          z = 1.0f / (1.0f + expf(-z));
-        }
-        out[(size_t)row * N + n] = z;
+    for (int j = 0; j < 8; ++j) acc[j] = warp_sum(acc[j]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) part[warp][j] = acc[j];
+    }
+    __syncthreads();
+    const int n = n0 + threadIdx.x;
+    if (threadIdx.x < 8 && n < N) {
+      float z = ((part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x])) + (bias ? bias[n] : 0.f);
+      if (mode == 1) {
+        z = cap * tanhf(z / cap);
+        if (n >= N / 2) z = log_sigmoid(z);
+      } else if (mode == 2) {
+        z = 1.0f / (1.0f + expf(-z));
       }
+      out[(size_t)row * N + n] = z;
+    }
+  }
+}
+
+// The same projection for FEW rows (M <= 64: decoded tokens, the rows whose logits are wanted): one warp per output n reads
+// its weight row with 128-bit loads and serves the rows eight at a time (the row is re-read from L1 for the next eight);
+// memory-bound on the weights.
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(128) linear_fewrows_kernel(const TA* __restrict__ A, long long lda, long long sA, const TW* __restrict__ Wt,
+                                                             long long ldw, long long sW, TC* __restrict__ C, long long ldc, long long sC, int M,
+                                                             int N, int K, float scale) {
+  const int b = blockIdx.y;
+  A += (size_t)b * sA;
+  Wt += (size_t)b * sW;
+  C += (size_t)b * sC;
+  const int n = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= N) return;
+  const TW* wr = Wt + (size_t)n * ldw;
+  const bool va = vec_ok(A, lda) && (sA * (long long)sizeof(TA)) % 16 == 0, vw = vec_ok(Wt, ldw) && (sW * (long long)sizeof(TW)) % 16 == 0;
+  for (int m0 = 0; m0 < M; m0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+    for (int k = lane * 8; k < K; k += 32 * 8) {
+      float wv[8], av[8];
+      load8(wr, k, K, vw, wv);
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        if (m0 + m < M) {
+          load8(A + (size_t)(m0 + m) * lda, k, K, va, av);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[m] = fmaf(av[i], wv[i], acc[m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const float sum = warp_sum(acc[m]);
+      if (lane == 0 && m0 + m < M) stf(C + (size_t)(m0 + m) * ldc + n, sum * scale);
     }
   }
 }
@@ -229,6 +303,17 @@ __global__ void __launch_bounds__(256) argmax_f32_kernel(const float* __restrict
 template <typename TA, typename TW>
 int launch_plain(const void* A, long long lda, long long sA, const void* W, long long ldw, long long sW, void* C, long long ldc, long long sC,
                  int M, int N, int K, int batch, float scale, int c_f32, cudaStream_t stream) {
+  if (M <= 64) {
+    dim3 g2((N + 3) / 4, batch);
+    if (c_f32)
+      linear_fewrows_kernel<TA, TW, float><<<g2, 128, 0, stream>>>(reinterpret_cast<const TA*>(A), lda, sA, reinterpret_cast<const TW*>(W), ldw, sW,
+                                                                   reinterpret_cast<float*>(C), ldc, sC, M, N, K, scale);
+    else
+      linear_fewrows_kernel<TA, TW, bf16><<<g2, 128, 0, stream>>>(reinterpret_cast<const TA*>(A), lda, sA, reinterpret_cast<const TW*>(W), ldw, sW,
+                                                                  reinterpret_cast<bf16*>(C), ldc, sC, M, N, K, scale);
+    LIA_LAUNCH_CHECK();
+    return LIA_OK;
+  }
   dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
   if (c_f32)
     linear_plain_kernel<TA, TW, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const TA*>(A), lda, sA, reinterpret_cast<const TW*>(W), ldw, sW,
@@ -307,7 +392,7 @@ extern "C" int lia_linear_small(const void* a, int a_f32, int lda, const void* w
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(a && w && out && M > 0 && N > 0 && K > 0 && lda >= K, "lia_linear_small: bad arguments");
   LIA_CHECK_ARG(mode >= 0 && mode <= 2 && (mode != 1 || (N % 2 == 0 && cap > 0.f)), "lia_linear_small: bad mode %d (N=%d cap=%f)", mode, N, cap);
-  const int grid = (M + 3) / 4;
+  const int grid = M;
   if (a_f32 && w_f32) linear_small_kernel<float, float><<<grid, 128, 0, stream>>>(reinterpret_cast<const float*>(a), lda, reinterpret_cast<const float*>(w), bias, out, M, N, K, mode, cap);
   else if (a_f32) linear_small_kernel<float, bf16><<<grid, 128, 0, stream>>>(reinterpret_cast<const float*>(a), lda, reinterpret_cast<const bf16*>(w), bias, out, M, N, K, mode, cap);
   else if (w_f32) linear_small_kernel<bf16, float><<<grid, 128, 0, stream>>>(reinterpret_cast<const bf16*>(a), lda, reinterpret_cast<const float*>(w), bias, out, M, N, K, mode, cap);

@@ -54,7 +54,7 @@ class Engine:
         d_segs = dev[o:o + n_seg].view(-1, 4)
         d_meta = dev[o + n_seg:o + n_seg + n_meta].view(-1, 2)
         d_want = dev[o + n_seg + n_meta:words] if n_want else None
-        return d_ids, StepBatch(n_ids, d_segs, d_meta), d_want
+        return d_ids, StepBatch(n_ids, d_segs, d_meta, max(s[1] + s[3] for s in segs)), d_want
 
     def _passes(self, entries):
         """Cut the step's entries into passes of at most ``max_rows`` rows; an entry longer than the budget continues in

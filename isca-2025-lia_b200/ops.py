@@ -434,13 +434,25 @@ def latent_prep(q, dkv, c_norm_w, inv_freq, meta, cache, qa, H, dim, rot, rot_di
     count_launches()
 
 
-def latent_attn(qa, cache, meta, gate, out, H, kv_rank, rot, scale):
-    """Causal softmax attention of every row over its sequence's cached latent rows (csrc/latent_attn.cu)."""
+def latent_attn_splits(M, H, max_ctx, sms):
+    """Key ranges per row: 1 when the rows alone fill the GPU (prompts), more when a few rows face a long history."""
+    blocks = M * ((H + 7) // 8)
+    want = (2 * sms + blocks - 1) // blocks
+    return max(1, min(want, 32, max_ctx // 64))
+
+
+def latent_attn(qa, cache, meta, gate, out, H, kv_rank, rot, scale, max_ctx=0):
+    """Causal softmax attention of every row over its sequence's cached latent rows (csrc/latent_attn.cu).  ``max_ctx``: an
+    upper bound of the rows' history lengths (0: unknown, no split of the keys)."""
     _req(qa, "qa", F32); _req(meta, "meta", torch.int32); _req(out, "out", F32)
     if gate is not None:
         _req(gate, "gate", F32)
     M = qa.shape[0]
-    check(_lib.load().lia_latent_attn(_p(qa), _p(cache), _f32(cache), cache.stride(0), _p(meta), _p(gate), _p(out), M, H, kv_rank, rot,
-                                      float(scale), _stream()), "lia_latent_attn")
-    count_launches()
+    nsplit = latent_attn_splits(M, H, max_ctx, _sm_count(qa.device))
+    ws = None
+    if nsplit > 1:
+        ws = torch.empty(_lib.load().lia_latent_attn_workspace_floats(M, H, kv_rank, nsplit), dtype=F32, device=qa.device)
+    check(_lib.load().lia_latent_attn(_p(qa), _p(cache), _f32(cache), cache.stride(0), _p(meta), _p(gate), _p(out), _p(ws), nsplit, M, H,
+                                      kv_rank, rot, float(scale), _stream()), "lia_latent_attn")
+    count_launches(2 if nsplit > 1 else 1)
     return out

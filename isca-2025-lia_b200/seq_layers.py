@@ -24,8 +24,9 @@ class StepBatch:
     """The token rows of one step: ``segs`` int32 [n, 4] = (slot, first position, first row, rows) per portion and
     ``meta`` int32 [rows, 2] = (slot, position) per row, both on the device."""
 
-    def __init__(self, rows, segs, meta):
+    def __init__(self, rows, segs, meta, max_ctx=0):
         self.rows, self.segs, self.meta = rows, segs, meta
+        self.max_ctx = max_ctx              # longest history (tokens cached after this step) among the step's sequences
 
 
 class Linear:
@@ -146,7 +147,7 @@ class LatentAttentionMixer:
         ops.linear_plain(q, self.w_uk_t, qa, batch=H, a_batch_stride=self.dim + self.rot, w_batch_stride=self.rank * self.dim,
                          out_batch_stride=D, n=self.rank, k=self.dim)
         lat = torch.empty(M, H * self.rank, dtype=F32, device=h.device)
-        ops.latent_attn(qa, cache, batch.meta, gate, lat, H, self.rank, self.rot, self.scale)
+        ops.latent_attn(qa, cache, batch.meta, gate, lat, H, self.rank, self.rot, self.scale, batch.max_ctx)
         o = torch.empty(M, H * self.vdim, dtype=self.dtype, device=h.device)
         ops.linear_plain(lat, self.w_uv, o, batch=H, a_batch_stride=self.rank, w_batch_stride=self.vdim * self.rank,
                          out_batch_stride=self.vdim, n=self.vdim, k=self.rank)
