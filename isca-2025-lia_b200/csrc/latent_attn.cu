@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
   float* alpha = ps + HG * TK;       // [HG]
   float* lsum = alpha + HG;          // [HG]
   float* msum = lsum + HG;           // [HG]
+  float* red = msum + HG;            // [8 warps][HG][TK] partial dot products
   const int row = blockIdx.x, h0 = blockIdx.y * HG, z = blockIdx.z, nsplit = gridDim.z;
   const int nh = min(HG, H - h0);
   const int slot = meta[2 * row], pos = meta[2 * row + 1];
@@ -150,15 +151,32 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
       }
     }
     __syncthreads();
-    if (warp < nh) {                             // warp = head, lane = key: a full dot product per lane, then the running softmax
-      const float4* q4 = reinterpret_cast<const float4*>(qs + warp * DS);
+    {
+      // lane = key.  Every warp takes each 8th group of 4 channels for ALL heads of the block, so a staged key row is read
+      // from shared memory once per tile and not once per head; the 8 partial sums of a (head, key) meet in `red`.
       const float4* k4 = reinterpret_cast<const float4*>(ks + lane * DS);
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-      for (int g = 0; g < G4; ++g) {
-        const float4 a = q4[g], b = k4[g];
-        d0 = fmaf(a.x, b.x, d0); d1 = fmaf(a.y, b.y, d1); d2 = fmaf(a.z, b.z, d2); d3 = fmaf(a.w, b.w, d3);
+      float pd[HG];
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) pd[hh] = 0.f;
+      for (int g = warp; g < G4; g += 8) {
+        const float4 b = k4[g];
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+          if (hh < nh) {
+            const float4 a = reinterpret_cast<const float4*>(qs + hh * DS)[g];
+            pd[hh] = fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, fmaf(a.w, b.w, pd[hh]))));
+          }
+        }
       }
-      const float sc = lane < nk ? ((d0 + d1) + (d2 + d3)) * scale : -INFINITY;
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) red[(warp * HG + hh) * TK + lane] = pd[hh];
+    }
+    __syncthreads();
+    if (warp < nh) {                             // warp = head: the partial sums in a fixed order, then the running softmax
+      float dot = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) dot += red[(w * HG + warp) * TK + lane];
+      const float sc = lane < nk ? dot * scale : -INFINITY;
       const float m_new = fmaxf(m_run, warp_max(sc));          // finite: the stage holds at least one visible key
       const float pr = expf(sc - m_new);
       const float a = expf(m_run - m_new);
@@ -247,7 +265,7 @@ template <typename T, int RM>
 int launch_attn(const float* qa, const void* cache, long long slot_stride, const int* meta, const float* gate, float* out, float* ws, int nsplit,
                 int M, int H, int kv_rank, int rot, float scale, cudaStream_t stream) {
   const int DS = padded_row(kv_rank + rot);
-  const size_t smem = ((size_t)HG * DS + (size_t)TK * DS + HG * TK + 3 * HG) * sizeof(float);
+  const size_t smem = ((size_t)HG * DS + (size_t)TK * DS + HG * TK + 3 * HG + 8 * HG * TK) * sizeof(float);
   LIA_CHECK_ARG(smem <= 200 * 1024, "lia_latent_attn: a cache row of %d numbers does not fit the shared-memory stage", kv_rank + rot);
   if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(latent_attn_kernel<T, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(M, (H + HG - 1) / HG, nsplit);

@@ -8,9 +8,9 @@
 // dim-long column a warp owns is contiguous.  Everything here is fp32 arithmetic on the CUDA cores; q, k, v arrive as the
 // projection wrote them (bf16 or fp32).
 //
-// Work split: a warp owns CW = 4 columns of S (4 value channels) of one head of one sequence and keeps them in registers
+// Work split: a warp owns CW = 2 columns of S (2 value channels) of one head of one sequence and keeps them in registers
 // for the whole portion; lane l owns rows l, l+32, ...  A token costs the warp DR*CW*2 FMAs per lane and one butterfly
-// reduction of CW+1 partial dot products; nothing is synchronised per token.  The 4 warps of a block share q, k and the
+// reduction of CW+1 partial dot products; nothing is synchronised per token.  The 8 warps of a block share q, k and the
 // gates of their head through a double-buffered shared-memory stage of TB = 8 tokens that is fetched while the previous
 // 8 tokens are processed.
 #include <math.h>
@@ -22,30 +22,40 @@ namespace {
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
 template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
-// loads that stay where they are written: issued at the top of a stage, consumed after it (the compiler would otherwise sink
-// them to their first use and expose the whole memory latency once per stage)
-__device__ __forceinline__ float ld_early(const float* p) {
-  float v;
-  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ float ld_early(const bf16* p) {
-  unsigned short u;
-  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(u) : "l"(p));
-  return __uint_as_float((unsigned)u << 16);
-}
+// Stage loads stay where they are written (volatile asm) and return RAW bits: nothing touches the loaded register until the
+// stage is stored to shared memory, so all loads of a stage are in flight together while the previous stage is processed.
+// (A conversion right after each load would make the warp wait for every load in turn.)
+template <typename T> struct Raw;
+template <> struct Raw<float> {
+  typedef float type;
+  static __device__ __forceinline__ float ld(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+  }
+  static __device__ __forceinline__ float to_float(float v) { return v; }
+};
+template <> struct Raw<bf16> {
+  typedef unsigned short type;
+  static __device__ __forceinline__ unsigned short ld(const bf16* p) {
+    unsigned short u;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(u) : "l"(p));
+    return u;
+  }
+  static __device__ __forceinline__ float to_float(unsigned short u) { return __uint_as_float((unsigned)u << 16); }
+};
 template <typename T> __device__ __forceinline__ void stf(T* p, float v);
 template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 constexpr int TB = 8;            // tokens per stage
-constexpr int CW = 4;            // columns of S per warp
-constexpr int NW = 4;            // warps per block
+constexpr int CW = 2;            // columns of S per warp
+constexpr int NW = 8;            // warps per block (two per scheduler: one warp alone cannot hide its own dependent-issue latency)
 constexpr int CB = CW * NW;      // columns per block
 
 // segs[s] = {slot, first position, first row, rows} of portion s
 template <typename T, int DR>
-__global__ void __launch_bounds__(NW * 32) mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
+__global__ void __launch_bounds__(NW * 32, 2) mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
                                                              const float* __restrict__ gates, float* __restrict__ St, float* __restrict__ nst,
                                                              float* __restrict__ mst, const int* __restrict__ segs, int H, int dim, int vdim,
                                                              float q_scale, float den_eps, float* __restrict__ o) {
@@ -70,39 +80,44 @@ __global__ void __launch_bounds__(NW * 32) mlstm_scan_kernel(const T* __restrict
   }
   float m = mst[(size_t)slot * H + h];
 
-  float buf[NST];
-  // fetch the inputs of tokens [g*TB, g*TB+TB) of the portion into registers
+  typename Raw<T>::type buf[NST];
+  float gbuf = 0.f;
+  // fetch the inputs of tokens [g*TB, g*TB+TB) of the portion into registers: q | k | v elements by all threads (one
+  // predicated load site, no use of the result), the 2 gates of each token by the first 2*TB threads
   auto fetch = [&](int g) {
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
       const int e = threadIdx.x + s * NW * 32;
-      float val = 0.f;
+      const T* p = nullptr;
       if (e < TB * ROWF) {
         const int t = e / ROWF, j = e - t * ROWF;
         const int tok = g * TB + t;
         if (tok < len) {
           const size_t row = (size_t)(row0 + tok);
-          if (j < DP) {
-            if (j < dim) val = ld_early(q + row * ld + h * dim + j);
-          } else if (j < 2 * DP) {
-            if (j - DP < dim) val = ld_early(k + row * ld + h * dim + (j - DP));
-          } else if (j < 2 * DP + CB) {
-            const int c = colb + j - 2 * DP;
-            if (c < vdim) val = ld_early(v + row * ld + h * vdim + c);
-          } else {
-            val = ld_early(gates + row * 2 * H + (j - 2 * DP - CB) * H + h);
-          }
+          if (j < dim) p = q + row * ld + h * dim + j;
+          else if (j >= DP && j - DP < dim) p = k + row * ld + h * dim + (j - DP);
+          else if (j >= 2 * DP && j < 2 * DP + CB && colb + j - 2 * DP < vdim) p = v + row * ld + h * vdim + colb + (j - 2 * DP);
         }
       }
-      buf[s] = val;
+      buf[s] = typename Raw<T>::type(0);
+      if (p != nullptr) buf[s] = Raw<T>::ld(p);
+    }
+    if (threadIdx.x < 2 * TB) {
+      const int tok = g * TB + (threadIdx.x >> 1);
+      gbuf = 0.f;
+      if (tok < len) gbuf = Raw<float>::ld(gates + (size_t)(row0 + tok) * 2 * H + (threadIdx.x & 1) * H + h);
     }
   };
   auto put = [&](int b) {
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
       const int e = threadIdx.x + s * NW * 32;
-      if (e < TB * ROWF) stage[b * TB * ROWF + e] = buf[s];
+      if (e < TB * ROWF) {
+        const int j = e % ROWF;
+        if (j < 2 * DP + CB) stage[b * TB * ROWF + e] = Raw<T>::to_float(buf[s]);
+      }
     }
+    if (threadIdx.x < 2 * TB) stage[b * TB * ROWF + (threadIdx.x >> 1) * ROWF + 2 * DP + CB + (threadIdx.x & 1)] = gbuf;
   };
 
   const int groups = (len + TB - 1) / TB;
