@@ -163,9 +163,13 @@ def run(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=2048, decod
             ms = _timed(step, warmup=3, iters=new - 4)
             d[f"decode_b{B}_ms_per_step"] = round(ms, 3)
             d[f"decode_b{B}_tokens_per_s"] = round(B / ms * 1e3, 1)
+            eng.graphs = False                    # the timed steps above replay a CUDA graph; the per-kernel pass launches eagerly
+            ms = _timed(step, warmup=1, iters=2)
+            d[f"decode_b{B}_ms_per_step_eager"] = round(ms, 3)
             with Instrument() as ins:
                 ins.extra = {"_keys": B * (decode_ctx + new), "_ctx": B * (decode_ctx + new)}
                 step()
+            eng.graphs = True
             d[f"decode_b{B}_kernels"] = ins.table(pk)
             eng.step([], end=ids)
         rec["davasun"] = d

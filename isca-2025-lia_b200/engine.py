@@ -8,26 +8,45 @@ batch, cuts what exceeds the row budget into further passes, runs the model's ``
 requests named in ``end``.  ``Engine.generate`` is greedy decoding on top of it (argmax on the device); the trace runner
 (bin/trace_run) drives the same ``step``.
 
+A pass in which every request brings ONE token (a decode step) is launch-bound when run eagerly -- some sixty kernels of
+a few microseconds each -- so it is captured as a CUDA graph the second time its shape comes up and replayed from then
+on: the ids, portions and positions live in one static device buffer that the pinned copy refreshes before every replay;
+the kernels read slots and positions from it, so one graph serves every step of that shape.  "Shape" is the number of
+rows, whether logits are wanted, and how many key ranges the attention splits a history into (``ops.latent_attn_splits``
+-- the only launch parameter that depends on the history's length).  The graph replays the very kernels of the eager pass;
+results are bit-identical.
+
 The reference serves one static batch per generate() call (greedy_search.py:37-460); this is the request-level face the
 step-wise models need.
 """
 import numpy as np
 import torch
 
-from . import ops
+from . import graphs, ops
 from .seq_layers import StepBatch
 
 
+class _StepGraph:
+    """One captured decode pass: the static input buffer, the graph and the logits it writes."""
+
+    def __init__(self, words, device):
+        self.inputs = torch.zeros(max(words, 2), dtype=torch.int32, device=device)
+        self.graph = None
+        self.logits = None
+
+
 class Engine:
-    def __init__(self, model, max_tokens, max_requests=4, max_rows=4096):
+    def __init__(self, model, max_tokens, max_requests=4, max_rows=4096, graphs=True):
         self.model = model
         self.max_rows = int(max_rows)
+        self.graphs = bool(graphs) and model.device.type == "cuda"     # decode passes as CUDA graphs (module docstring)
+        self._step_graphs = {}
         self.slots = model.new_state(int(max_requests), int(max_tokens))
         self.device = model.device
         self._host = self._copied = None
 
     # ---- batch assembly: one pinned staging buffer, one H2D copy per pass
-    def _upload(self, ids, segs, meta, want):
+    def _upload(self, ids, segs, meta, want, static=None):
         n_ids, n_seg, n_meta, n_want = len(ids), len(segs) * 4, len(meta) * 2, len(want)
         words = 2 * n_ids + n_seg + n_meta + n_want
         if self._host is None or self._host.numel() < words:
@@ -45,7 +64,11 @@ class Engine:
         a[o + n_seg:o + n_seg + n_meta] = np.asarray(meta, dtype=np.int32).reshape(-1)
         if n_want:
             a[o + n_seg + n_meta:words] = np.asarray(want, dtype=np.int32)
-        dev = host.to(self.device, non_blocking=True)
+        if static is not None:
+            dev = static[:host.numel()]
+            dev.copy_(host, non_blocking=True)
+        else:
+            dev = host.to(self.device, non_blocking=True)
         if self._copied is not None:
             self._copied.record()
         elif dev.data_ptr() == host.data_ptr():
@@ -72,6 +95,31 @@ class Engine:
                     cur, rows = [], 0
         if cur:
             yield cur
+
+    # ---- decode passes as CUDA graphs
+    def _graph_key(self, group, segs, want):
+        """The shape of a pass that may run as a graph (None: run it eagerly): every portion is one token, logits are wanted
+        for all rows or for none, and the key carries what the launches depend on besides the static buffers' contents."""
+        n = len(group)
+        if not self.graphs or any(len(toks) != 1 for _, toks, _ in group) or len(want) not in (0, n):
+            return None
+        return (n, len(want), ops.latent_attn_split_class(max(s[1] + s[3] for s in segs)))
+
+    def _run_graphed(self, key, ids, segs, meta, want):
+        g = self._step_graphs.get(key)
+        if g is None:
+            # first time: run eagerly (this also warms every workspace the pass allocates outside the graph's pool)
+            self._step_graphs[key] = _StepGraph(2 * len(ids) + 4 * len(segs) + 2 * len(meta) + len(want), self.device)
+            d_ids, batch, d_want = self._upload(ids, segs, meta, want)
+            return self.model.forward_rows(d_ids, batch, d_want, self.slots)
+        d_ids, batch, d_want = self._upload(ids, segs, meta, want, static=g.inputs)
+        if g.graph is None:
+            graph = torch.cuda.CUDAGraph()
+            with graphs.capture(graph):
+                g.logits = self.model.forward_rows(d_ids, batch, d_want, self.slots)
+            g.graph = graph
+        g.graph.replay()
+        return g.logits.clone() if g.logits is not None else None
 
     def step(self, entries, end=(), trace=None):
         """entries: dicts ``{"id", "tokens", "want"}``; returns fp32 logits [wanted places, vocab] in the order of the entries
@@ -101,8 +149,12 @@ class Engine:
                 want += [row + i for i in w]
                 ids += toks
                 row += len(toks)
-            d_ids, batch, d_want = self._upload(ids, segs, meta, want)
-            logits = self.model.forward_rows(d_ids, batch, d_want, self.slots, trace=trace)
+            key = self._graph_key(group, segs, want) if trace is None else None
+            if key is not None:
+                logits = self._run_graphed(key, ids, segs, meta, want)
+            else:
+                d_ids, batch, d_want = self._upload(ids, segs, meta, want)
+                logits = self.model.forward_rows(d_ids, batch, d_want, self.slots, trace=trace)
             if logits is not None:
                 outs.append(logits)
         for rid in end:

@@ -434,11 +434,19 @@ def latent_prep(q, dkv, c_norm_w, inv_freq, meta, cache, qa, H, dim, rot, rot_di
     count_launches()
 
 
+LATENT_SPLIT_KEYS, LATENT_MAX_SPLITS = 64, 32
+
+
+def latent_attn_split_class(max_ctx):
+    """All that ``latent_attn_splits`` takes from the history's length: two lengths of one class launch alike."""
+    return min(max_ctx // LATENT_SPLIT_KEYS, LATENT_MAX_SPLITS)
+
+
 def latent_attn_splits(M, H, max_ctx, sms):
     """Key ranges per row: 1 when the rows alone fill the GPU (prompts), more when a few rows face a long history."""
     blocks = M * ((H + 7) // 8)
     want = (2 * sms + blocks - 1) // blocks
-    return max(1, min(want, 32, max_ctx // 64))
+    return max(1, min(want, latent_attn_split_class(max_ctx)))
 
 
 def latent_attn(qa, cache, meta, gate, out, H, kv_rank, rot, scale, max_ctx=0):

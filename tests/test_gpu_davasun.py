@@ -423,6 +423,38 @@ def test_long_decoding_keeps_the_state_exact():
     assert err(torch.cat(outs), want) < 2e-4
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_graphed_decode_passes_equal_eager_ones_bit_for_bit(dtype):
+    """Decode passes replayed as CUDA graphs against the same passes launched one kernel at a time: two requests of unequal
+    history whose lengths cross the 64- and 128-key borders at which the attention changes its split of the keys, steps
+    that want no logits, a request that ends and another that takes over its slot while the graphs stay in use."""
+    cfg, w, m = build("even", dtype)
+    a, b, c = toks_for(cfg, 179, 40), toks_for(cfg, 110, 41), toks_for(cfg, 30, 42)
+
+    def play(graphs):
+        eng = Engine(m, 180, 2, graphs=graphs)
+        outs = [eng.step([{"id": "a", "tokens": a[:50], "want": [49]}, {"id": "b", "tokens": b[:3], "want": [2]}])]
+        for i in range(100):
+            want = [] if i % 7 == 3 else [0]
+            o = eng.step([{"id": "a", "tokens": [a[50 + i]], "want": want}, {"id": "b", "tokens": [b[3 + i]], "want": want}])
+            assert (o is None) == (not want)
+            if o is not None:
+                outs.append(o)
+        eng.step([], end=["b"])
+        outs.append(eng.step([{"id": "c", "tokens": c[:1], "want": [0]}]))           # b's slot, state zeroed; alone in its pass
+        for i in range(1, 30):
+            outs.append(eng.step([{"id": "c", "tokens": [c[i]], "want": [0]}, {"id": "a", "tokens": [a[149 + i]], "want": [0]}]))
+        return torch.cat(outs), eng
+
+    eager, _ = play(False)
+    graphed, eng = play(True)
+    assert sum(g.graph is not None for g in eng._step_graphs.values()) >= 4           # several shapes were captured and replayed
+    assert torch.equal(eager, graphed)
+    if dtype == F32:
+        la, lc = oracle_logits(cfg, w, a), oracle_logits(cfg, w, c)
+        assert err(graphed[-2:-1], lc[29:30]) < 2e-4 and err(graphed[-1:], la[178:179]) < 2e-4      # the last pass: c, then a
+
+
 def test_first_tokens_and_single_token_prompts():
     cfg, w, m = build("wide", F32)
     eng = Engine(m, 8, 3)
