@@ -491,7 +491,7 @@ def _main(args, json_out):
     elif not args.no_parity:
         try:
             parity = parity_check(m, cfg, args, st, ids_dev, out, rank, world, dev)
-        except torch.OutOfMemoryError as e:      # the checker must never cost the line its throughput numbers
+        except torch.OutOfMemoryError as e:      # the parity comparison must never cost the line its throughput numbers
             parity = {"skipped": f"oracle ran out of memory: {str(e)[:120]}"}
             if dev.type == "cuda":
                 torch.cuda.empty_cache()

@@ -229,7 +229,7 @@ lia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       if (sig_data_u >= 0 || sig_done_u >= 0) {
         // The CTA barrier orders every epilogue thread's stores of the covered tile before the signalling threads, whose
         // st.release.sys is the release pattern that publishes them (release is cumulative over what the barrier made
-        // visible to the storing thread).  Round 1 had all 128 threads execute a system-scope fence here first: ~8 us per
+        // visible to the storing thread).  An earlier version had all 128 threads execute a system-scope fence here first: ~8 us per
         // tile, 100 us per launch of a short-K projection where no MMA time hides it (scripts/tp_microbench.py, TP2
         // out_proj prefill: 509 -> 405 us).
         epi_bar_sync();

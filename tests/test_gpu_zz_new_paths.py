@@ -1,4 +1,4 @@
-"""GPU checks of the paths added after the round-1 GPU budget was spent -- the only GPU tests that had not yet run on
+"""GPU checks of the paths that were added last -- the only GPU tests that had not yet run on
 hardware when committed, which is why the file is named to run after the others.  Each path re-uses the kernels the
 other GPU files verify, in a new order or layout whose HOST side is pinned bit-exactly on CPU (tests/test_host_model_cpu.py,
 tests/test_kv_spill.py):

@@ -81,7 +81,7 @@ def main():
     cfg = lia_b200.OPTConfig(hidden_size=512, num_hidden_layers=4, num_attention_heads=8, ffn_dim=2048, vocab_size=1024,
                              max_position_embeddings=128)
     # (8, 40, nmb 2): 160-row prefill blocks (two-shot, M > 128); (4, 24, nmb 1): a 96-row prefill, which runs on the
-    # decode-shaped (swap-AB, M <= 128) kernels with S > 1 -- the case that overran the decode residual buffer in round 1
+    # decode-shaped (swap-AB, M <= 128) kernels with S > 1 -- the case that once overran the decode residual buffer
     for (B, S, new, nmb) in [(8, 40, 8, 2), (4, 24, 6, 1)]:
         _model_case(lia_b200, tp, dist, cfg, dev, rank, world, B, S, new, nmb)
     dist.barrier()
