@@ -112,6 +112,29 @@ def test_engine_lays_out_entries_and_cuts_passes():
         e.step([{"id": "z", "tokens": [1], "want": [1]}])
 
 
+def test_engine_graph_key_names_what_a_decode_pass_launch_depends_on():
+    """Which passes may replay a captured graph, and which of them may share one: only passes of single tokens, with logits
+    wanted for all rows or none; the key separates row counts, the wanted pattern and the attention's key-split class, and
+    the split count itself depends on a history's length through that class alone."""
+    from lia_b200 import ops
+    e = Engine(_Recorder(), max_tokens=4096, max_requests=4)
+    assert e.graphs is False and e._graph_key([(0, [1], [0])], [(0, 5, 0, 1)], [0]) is None      # no graphs off the GPU
+    e.graphs = True
+    one = lambda slot, p0, row: ((slot, [7], [0]), (slot, p0, row, 1))  # noqa: E731
+    (g0, s0), (g1, s1) = one(0, 10, 0), one(1, 200, 1)
+    assert e._graph_key([g0, g1], [s0, s1], [0, 1]) == (2, 2, ops.latent_attn_split_class(201))
+    assert e._graph_key([g0, g1], [s0, s1], []) == (2, 0, ops.latent_attn_split_class(201))
+    assert e._graph_key([g0, g1], [s0, s1], [1]) is None                                         # logits of some rows only
+    assert e._graph_key([g0, (1, [7, 8], [1])], [s0, (1, 200, 1, 2)], [0, 2]) is None            # a portion of two tokens
+    assert e._graph_key([g0], [s0], [0]) != e._graph_key([g0, g1], [s0, s1], [0, 1])
+    for ctx in (1, 63, 64, 65, 127, 128, 2047, 2048, 2049, 100000):
+        cls = ops.latent_attn_split_class(ctx)
+        same = [c for c in range(max(1, ctx - 70), ctx + 70) if ops.latent_attn_split_class(c) == cls]
+        for M, H, sms in ((1, 16, 148), (16, 32, 148), (3, 5, 8), (4096, 16, 148)):
+            assert len({ops.latent_attn_splits(M, H, c, sms) for c in same}) == 1
+            assert 1 <= ops.latent_attn_splits(M, H, ctx, sms) <= max(1, min(ops.LATENT_MAX_SPLITS, ctx // ops.LATENT_SPLIT_KEYS))
+
+
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_oracle_is_consistent_under_portions(name):
     """The oracle itself: one pass over a prompt equals portions of 1, 2 and more tokens through carried state."""
