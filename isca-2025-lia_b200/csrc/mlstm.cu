@@ -12,7 +12,9 @@
 // for the whole portion; lane l owns rows l, l+32, ...  A token costs the warp DR*CW*2 FMAs per lane and one butterfly
 // reduction of CW+1 partial dot products; nothing is synchronised per token.  The 8 warps of a block share q, k and the
 // gates of their head through a double-buffered shared-memory stage of TB = 8 tokens that is fetched while the previous
-// 8 tokens are processed.
+// 8 tokens are processed -- with 128-bit loads where the rows allow it: every block of a head re-reads that head's q and
+// k, and with one load instruction (and its address arithmetic) per number the fetch cost more issue slots than the
+// recurrence itself (2048 tokens, heads of 256 x 512: 1.24 -> 0.87 ms per layer).
 #include <math.h>
 
 #include "common.cuh"
@@ -44,6 +46,28 @@ template <> struct Raw<bf16> {
   }
   static __device__ __forceinline__ float to_float(unsigned short u) { return __uint_as_float((unsigned)u << 16); }
 };
+// 128-bit stage load (raw bits, same reasoning) and its unpacking into VEC floats of a 16-byte aligned shared-memory row
+__device__ __forceinline__ uint4 ld_raw128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+template <typename T> struct Vec128;
+template <> struct Vec128<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void put(float* dst, uint4 v) {
+    *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+  }
+};
+template <> struct Vec128<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void put(float* dst, uint4 v) {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                                                    __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+    reinterpret_cast<float4*>(dst)[1] = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                                                    __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+  }
+};
 template <typename T> __device__ __forceinline__ void stf(T* p, float v);
 template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
@@ -53,16 +77,19 @@ constexpr int CW = 2;            // columns of S per warp
 constexpr int NW = 8;            // warps per block (two per scheduler: one warp alone cannot hide its own dependent-issue latency)
 constexpr int CB = CW * NW;      // columns per block
 
-// segs[s] = {slot, first position, first row, rows} of portion s
-template <typename T, int DR>
+// segs[s] = {slot, first position, first row, rows} of portion s.  VL: the stage is fetched with 128-bit loads (the host
+// checked that every q / k / v segment of VEC numbers starts on a 16-byte boundary and is wholly inside or outside its row).
+template <typename T, int DR, bool VL>
 __global__ void __launch_bounds__(NW * 32, 2) mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
                                                              const float* __restrict__ gates, float* __restrict__ St, float* __restrict__ nst,
                                                              float* __restrict__ mst, const int* __restrict__ segs, int H, int dim, int vdim,
                                                              float q_scale, float den_eps, float* __restrict__ o) {
   constexpr int DP = DR * 32;                    // dim padded to whole warps
-  constexpr int ROWF = 2 * DP + CB + 2;          // floats of one staged token: q | k | v (this block's columns) | i | f
-  constexpr int NST = (TB * ROWF + NW * 32 - 1) / (NW * 32);
-  extern __shared__ float stage[];               // [2][TB][ROWF]
+  constexpr int ROWF = 2 * DP + CB + 4;          // floats of one staged token: q | k | v (this block's columns) | i | f | 2 pad (16-byte rows)
+  constexpr int VEC = Vec128<T>::N;
+  constexpr int CH = (2 * DP + CB) / VEC;        // 128-bit segments of one staged token
+  constexpr int NST = VL ? (TB * CH + NW * 32 - 1) / (NW * 32) : (TB * ROWF + NW * 32 - 1) / (NW * 32);
+  extern __shared__ __align__(16) float stage[]; // [2][TB][ROWF]
   const int seg = blockIdx.z, h = blockIdx.y, colb = blockIdx.x * CB;
   const int slot = segs[4 * seg], row0 = segs[4 * seg + 2], len = segs[4 * seg + 3];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,11 +107,31 @@ __global__ void __launch_bounds__(NW * 32, 2) mlstm_scan_kernel(const T* __restr
   }
   float m = mst[(size_t)slot * H + h];
 
-  typename Raw<T>::type buf[NST];
+  typename Raw<T>::type buf[VL ? 1 : NST];
+  uint4 vbuf[VL ? NST : 1];
   float gbuf = 0.f;
   // fetch the inputs of tokens [g*TB, g*TB+TB) of the portion into registers: q | k | v elements by all threads (one
   // predicated load site, no use of the result), the 2 gates of each token by the first 2*TB threads
   auto fetch = [&](int g) {
+    if constexpr (VL) {
+#pragma unroll
+      for (int s = 0; s < NST; ++s) {
+        const int e = threadIdx.x + s * NW * 32;
+        const T* p = nullptr;
+        if (e < TB * CH) {
+          const int t = e / CH, j = (e - t * CH) * VEC;
+          const int tok = g * TB + t;
+          if (tok < len) {
+            const size_t row = (size_t)(row0 + tok);
+            if (j < DP) { if (j < dim) p = q + row * ld + h * dim + j; }
+            else if (j < 2 * DP) { if (j - DP < dim) p = k + row * ld + h * dim + (j - DP); }
+            else if (colb + j - 2 * DP < vdim) p = v + row * ld + h * vdim + colb + (j - 2 * DP);
+          }
+        }
+        vbuf[s] = make_uint4(0u, 0u, 0u, 0u);
+        if (p != nullptr) vbuf[s] = ld_raw128(p);
+      }
+    } else {
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
       const int e = threadIdx.x + s * NW * 32;
@@ -102,6 +149,7 @@ __global__ void __launch_bounds__(NW * 32, 2) mlstm_scan_kernel(const T* __restr
       buf[s] = typename Raw<T>::type(0);
       if (p != nullptr) buf[s] = Raw<T>::ld(p);
     }
+    }
     if (threadIdx.x < 2 * TB) {
       const int tok = g * TB + (threadIdx.x >> 1);
       gbuf = 0.f;
@@ -109,6 +157,16 @@ __global__ void __launch_bounds__(NW * 32, 2) mlstm_scan_kernel(const T* __restr
     }
   };
   auto put = [&](int b) {
+    if constexpr (VL) {
+#pragma unroll
+      for (int s = 0; s < NST; ++s) {
+        const int e = threadIdx.x + s * NW * 32;
+        if (e < TB * CH) {
+          const int t = e / CH, j = (e - t * CH) * VEC;
+          Vec128<T>::put(stage + b * TB * ROWF + t * ROWF + j, vbuf[s]);
+        }
+      }
+    } else {
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
       const int e = threadIdx.x + s * NW * 32;
@@ -116,6 +174,7 @@ __global__ void __launch_bounds__(NW * 32, 2) mlstm_scan_kernel(const T* __restr
         const int j = e % ROWF;
         if (j < 2 * DP + CB) stage[b * TB * ROWF + e] = Raw<T>::to_float(buf[s]);
       }
+    }
     }
     if (threadIdx.x < 2 * TB) stage[b * TB * ROWF + (threadIdx.x >> 1) * ROWF + 2 * DP + CB + (threadIdx.x & 1)] = gbuf;
   };
@@ -196,16 +255,26 @@ __global__ void __launch_bounds__(128) headnorm_gate_kernel(const float* __restr
   }
 }
 
-template <typename T, int DR>
-int launch_scan(const void* q, const void* k, const void* v, int ld, const float* gates, float* St, float* nst, float* mst, const int* segs,
+template <typename T, int DR, bool VL>
+int launch_scan_as(const void* q, const void* k, const void* v, int ld, const float* gates, float* St, float* nst, float* mst, const int* segs,
                 int nseg, int H, int dim, int vdim, float q_scale, float den_eps, float* o, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * TB * (2 * DR * 32 + CB + 2) * sizeof(float);
-  if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<T, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const size_t smem = (size_t)2 * TB * (2 * DR * 32 + CB + 4) * sizeof(float);
+  if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<T, DR, VL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((vdim + CB - 1) / CB, H, nseg);
-  mlstm_scan_kernel<T, DR><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), reinterpret_cast<const T*>(v),
+  mlstm_scan_kernel<T, DR, VL><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), reinterpret_cast<const T*>(v),
                                                             ld, gates, St, nst, mst, segs, H, dim, vdim, q_scale, den_eps, o);
   LIA_LAUNCH_CHECK();
   return LIA_OK;
+}
+
+template <typename T, int DR>
+int launch_scan(const void* q, const void* k, const void* v, int ld, const float* gates, float* St, float* nst, float* mst, const int* segs,
+                int nseg, int H, int dim, int vdim, float q_scale, float den_eps, float* o, cudaStream_t stream) {
+  constexpr int VEC = Vec128<T>::N;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) % 16 == 0) &&
+                       ld % VEC == 0 && dim % VEC == 0 && vdim % VEC == 0;
+  if (aligned) return launch_scan_as<T, DR, true>(q, k, v, ld, gates, St, nst, mst, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
+  return launch_scan_as<T, DR, false>(q, k, v, ld, gates, St, nst, mst, segs, nseg, H, dim, vdim, q_scale, den_eps, o, stream);
 }
 
 template <typename T>

@@ -176,9 +176,10 @@ def test_mlstm_scan_against_the_token_loop(H, d, e, T):
         assert torch.equal(state2[0], state[0]) and torch.equal(state2[2], state[2])
 
 
-def test_mlstm_scan_batches_of_unequal_portions_and_bf16_inputs():
+@pytest.mark.parametrize("d,e", [(24, 40), (12, 21), (64, 16)])          # 128-bit stage loads; element-wise ones; one column block
+def test_mlstm_scan_batches_of_unequal_portions_and_bf16_inputs(d, e):
     g = gen(6)
-    H, d, e, lens = 2, 24, 40, [5, 1, 19, 8]
+    H, lens = 2, [5, 1, 19, 8]
     T = sum(lens)
     q, k, v = torch.randn(T, H, d, generator=g), torch.randn(T, H, d, generator=g), torch.randn(T, H, e, generator=g)
     ig, fg = torch.randn(T, H, generator=g), -torch.rand(T, H, generator=g)
