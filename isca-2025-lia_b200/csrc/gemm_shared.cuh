@@ -477,7 +477,7 @@ __device__ __forceinline__ void swap_epilogue_tile(const EpiParams& p, const Swa
     if (n_ok) {
       constexpr int RB = ITERS < 4 ? ITERS : 4;
       // (a real loop, not unrolled: this code runs once per tile and its size is paid in instruction-cache
-      // misses -- the unrolled epilogue was ~120 KB of SASS)
+      // misses -- the unrolled epilogue was ~120 KB of machine code)
 #pragma unroll 1
       for (int it0 = 0; it0 < ITERS; it0 += RB) {
         uint4 rcur[RB];      // this batch's prefetched residual rows (register select, no dynamic indexing)
