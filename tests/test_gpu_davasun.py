@@ -492,3 +492,46 @@ def test_greedy_generation_through_generate_and_from_pretrained(tmp_path):
             if float(top.values[0] - top.values[1]) > 1e-3:
                 assert int(out[b, 12 + t]) == int(top.indices[0]), (b, t)
                 assert int(out_chunked[b, 12 + t]) == int(out[b, 12 + t])
+
+
+def _write_checkpoint(tmp_path, cfg, seed):
+    w = O.random_weights(DavasunConfig.from_dict(cfg).tensor_shapes(), seed)
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(d / "model.safetensors"), {k: v.to(BF16) for k, v in w.items()})
+    return str(d), w
+
+
+def test_trace_runner_and_command_line_as_a_user_calls_them(tmp_path):
+    """The two programs a user runs, as child processes on a small checkpoint: the trace runner (steps on standard input,
+    one logits file per step that wants some, 'done <step>' lines, slots given back by 'end') in both dtypes against the
+    oracle, and run.py's generation summary."""
+    import subprocess
+    import sys
+    import numpy as np
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = CASES["even"]
+    ckpt, w = _write_checkpoint(tmp_path, cfg, 15)
+    a, b = toks_for(cfg, 41, 50), toks_for(cfg, 6, 51)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[30:32], "want": []}], "end": []},              # nothing wanted: no file
+             {"step": 2, "entries": [{"id": "a", "tokens": a[32:40], "want": [7]}], "end": []}]
+    steps += [{"step": 3, "entries": [{"id": "a", "tokens": a[40:41], "want": [0]}], "end": ["a"]},
+              {"step": 4, "entries": [{"id": "b", "tokens": b, "want": [5]}], "end": ["b"]}]               # a's slot, handed out again
+    la, lb = oracle_logits(cfg, w, a), oracle_logits(cfg, w, b)
+    want = {0: la[[0, 29]], 2: la[[39]], 3: la[[40]], 4: lb[[5]]}
+    for dtype, tol in (("float32", 2e-4), ("bfloat16", 0.2)):
+        out = tmp_path / ("out_" + dtype)
+        p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", ckpt, "--dtype", dtype, "--out", str(out), "--max-tokens", "64"],
+                           input="".join(json.dumps(s) + "\n" for s in steps), text=True, capture_output=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == ["done %d" % s["step"] for s in steps]
+        assert sorted(os.listdir(out)) == ["%d.f32" % k for k in sorted(want)]
+        for k, ref in want.items():
+            got = torch.from_numpy(np.fromfile(out / ("%d.f32" % k), dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+            assert got.shape == ref.shape and err(got, ref) < tol, (dtype, k)
+    p = subprocess.run([sys.executable, os.path.join(root, "run.py"), "-m", ckpt, "--dtype", "float32", "--input-tokens", "9", "--max-new-tokens", "5",
+                        "--batch-size", "2", "--num-iter", "2", "--num-warmup", "1"], text=True, capture_output=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "Inference latency:" in p.stdout and "Throughput:" in p.stdout and "[5, 5]" in p.stdout
