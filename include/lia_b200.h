@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define LIA_ABI_VERSION 6
+#define LIA_ABI_VERSION 7
 
 typedef void* lia_stream_t; /* cudaStream_t */
 
@@ -286,9 +286,9 @@ int lia_argmax_f32(const float* logits, int64_t* next, int B, int V, int suppres
 int lia_mlstm_scan(const void* q, const void* k, const void* v, int act_f32, int ld, const float* gates, float* state_S, float* state_n,
                    float* state_m, const int* segs, int nseg, int H, int dim, int vdim, float q_scale, float den_eps, float* o,
                    lia_stream_t stream);
-/* out[row][h] = o[row][h] / rms_over_vdim * w[h] * sigmoid(gate[row][h]) */
+/* out[row][h] = o[row][h] / rms_over_vdim * w[h] * act(gate[row][h]), act = sigmoid (gate_silu == 0) or SiLU */
 int lia_headnorm_gate(const float* o, const float* w, const void* gate, int ldg, void* out, int act_f32, int M, int H, int vdim, float eps,
-                      lia_stream_t stream);
+                      int gate_silu, lia_stream_t stream);
 /* cache[slot][pos] = [rmsnorm(dkv[:kv_rank]) * c_norm_w | rotate(dkv[kv_rank:], pos)];  qa[row][h][kv_rank:] =
  * rotate(q[row][h][dim:], pos)  (qa rows are [H][kv_rank + rot] fp32; the caller fills qa[..][:kv_rank]) */
 int lia_latent_prep(const void* q, int ldq, const void* dkv, int ldd, int act_f32, const float* c_norm_w, const float* inv_freq,
@@ -300,6 +300,70 @@ int lia_latent_prep(const void* q, int ldq, const void* dkv, int ldd, int act_f3
 size_t lia_latent_attn_workspace_floats(int M, int H, int kv_rank, int nsplit);
 int lia_latent_attn(const float* qa, const void* cache, int cache_f32, long long slot_stride, const int* meta, const float* gate,
                     float* out, float* workspace, int nsplit, int M, int H, int kv_rank, int rot, float scale, lia_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Models whose sublayers sit between layer norms (weight and bias) on a 32-bit residual stream, with linear-attention
+ * recurrences (a fixed decay per head, or the gated delta rule behind a short convolution), sliding-window attention
+ * with grouped key/value heads, and dense or mixture-of-experts feed-forwards.  Same conventions as the section above.
+ * The reference has none of these. */
+enum { LIA_ACT_NONE = 0, LIA_ACT_RELU = 1, LIA_ACT_SILU = 2, LIA_ACT_GELU_ERF = 3, LIA_ACT_GELU_TANH = 4 };
+
+/* x[r] = table[ids[r]] as fp32; x_copy (may be NULL) receives the same rows */
+int lia_embed_rows(const int64_t* ids, const void* table, int table_f32, float* x, float* x_copy, int rows, int W, int vocab,
+                   lia_stream_t stream);
+/* if y: x += mult * (LN(y) * w_post + b_post);  if extra: x += extra;  if h: h = LN(x) * w_pre + b_pre.
+ * LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps), fp32. */
+int lia_ln_add_norm(float* x, const void* y, int y_f32, const float* w_post, const float* b_post, float mult, const float* extra,
+                    const float* w_pre, const float* b_pre, void* h, int h_f32, int rows, int W, float eps, lia_stream_t stream);
+int lia_ln_gather(const float* x, const int* rows, const float* w, const float* b, void* h, int h_f32, int n, int W, float eps,
+                  lia_stream_t stream);
+/* out[m][f] = act(in[m][f]) * in[m][up_off + f]; up_off < 0: out = act(in).  `in` has row stride ld. */
+int lia_gated_act(const void* in, int ld, int up_off, void* out, int act_f32, int M, int F, int act, lia_stream_t stream);
+
+/* softmax over E fp32 logits per row, the `top` largest (lowest index first on ties), divided by their sum + 1e-20 */
+int lia_router_topk(const float* logits, int* idx, float* wt, int M, int E, int top, lia_stream_t stream);
+/* (token, choice) pairs grouped by expert into tiles of lia_moe_tile_rows() rows: perm[n_tiles * rows] (pair or -1),
+ * tile_expert[n_tiles] (expert or -1), pos_of[pairs] (place of a pair in perm).
+ * n_tiles >= (pairs + min(E, pairs) * (rows - 1)) / rows. */
+int lia_moe_tile_rows(void);
+int lia_moe_plan(const int* idx, int pairs, int E, int n_tiles, int* perm, int* tile_expert, int* pos_of, lia_stream_t stream);
+/* One projection of every expert (weights [E][N][K], expert stride given) over its own rows.
+ * up != 0: C[place of pair] = act(A[pair / top] @ W[e].T), C of the activations' type;
+ * up == 0: C[pair] = wt[pair] * (A[place of pair] @ W[e].T), C fp32.
+ * perm == NULL: the few-rows form; a pair's place is the pair itself and idx[pair] names its expert. */
+int lia_moe_gemm(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
+                 const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N, int K,
+                 int up, int act, lia_stream_t stream);
+/* y[m] = sum_t ypair[m * top + t] (+ shared[m], may be NULL), fp32 */
+int lia_moe_combine(const float* ypair, const void* shared, int shared_f32, float* y, int M, int W, int top, lia_stream_t stream);
+
+/* Short causal convolution (taps <= 8, weights [channels][taps], last column = current token) + SiLU over the q | k | v
+ * channels of a projection's output y (row stride ld, column offsets given; q and k have G heads of dim, v has H of vdim);
+ * q and k divided by sqrt(sum of squares + unit_eps) per head, q times q_scale; gates [M][2H] hold W_b h | W_a h on entry and
+ * beta = sigmoid(.) | g = exp(-exp(a_log) * softplus(. + dt_bias)) on return.  conv_state [slot][taps-1][channels] fp32 holds
+ * the inputs before each portion; lia_conv_state_update (after lia_conv_prep) moves it past the step's portions. */
+int lia_conv_prep(const void* y, int y_f32, int ld, int q_off, int k_off, int v_off, const float* wconv, const float* conv_state,
+                  const int* meta, float* gates, const float* a_log, const float* dt_bias, float* qk, float* v, int M, int G, int H,
+                  int dim, int vdim, int taps, float q_scale, float unit_eps, lia_stream_t stream);
+int lia_conv_state_update(const void* y, int y_f32, int ld, int q_off, int k_off, int v_off, int nqk, int nv, float* conv_state,
+                          const int* segs, int nseg, int taps, lia_stream_t stream);
+/* Matrix-state recurrence over every portion; state_S [slot][H][vdim][dim] fp32, o [rows][H * vdim] fp32.
+ * gates == NULL:  S = decay[h] S + k v^T, o = S^T q.   gates [rows][2H] = beta | g:  the gated delta rule
+ * S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q.   q, k: G heads (head h reads h / (H / G)), row stride ldqk;
+ * in_silu != 0 applies SiLU to q, k, v as they are read. */
+int lia_linear_scan(const void* q, const void* k, int ldqk, const void* v, int ldv, int act_f32, int in_silu, const float* decay,
+                    const float* gates, float* state_S, const int* segs, int nseg, int H, int G, int dim, int vdim, float* o,
+                    lia_stream_t stream);
+
+/* keys as they are and values divided by their per-head root mean square (norm_values != 0) into the caches
+ * [slot][capacity][G * dim] and [slot][capacity][G * vdim] at meta[row] = {slot, position} */
+int lia_kv_store(const void* k, int ldk, const void* v, int ldv, int act_f32, const int* meta, void* kcache, long long k_slot_stride,
+                 void* vcache, long long v_slot_stride, int M, int G, int dim, int vdim, float eps, int norm_values, lia_stream_t stream);
+/* out[row][h] = sum_j softmax_j(cap(q[row][h] . k[j][h / (H/G)] * scale * temp[h])) v[j][h / (H/G)] over 0 <= pos - j < window,
+ * cap(s) = softcap * tanh(s / softcap) (softcap <= 0: none) */
+int lia_window_attn(const void* q, int ldq, int act_f32, const void* kcache, long long k_slot_stride, const void* vcache,
+                    long long v_slot_stride, const int* meta, const float* temp, void* out, int M, int H, int G, int dim, int vdim,
+                    int window, float scale, float softcap, lia_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libliab200.so")
 
 EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_RESIDUAL, EPI_QKV = 0, 1, 2, 3
-ABI_VERSION = 6
+ABI_VERSION = 7
 TP_MAX_WORLD = 8
 P2P_HANDLE_BYTES = 64
 
@@ -96,11 +96,33 @@ _PROTOTYPES = {
     "lia_argmax_f32": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "lia_mlstm_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p]),
-    "lia_headnorm_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_headnorm_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "lia_latent_prep": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
     "lia_latent_attn_workspace_floats": (c_size_t, [c_int, c_int, c_int, c_int]),
     "lia_latent_attn": (c_int, [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    # models between layer norms: decay / delta-rule recurrences, sliding-window attention, mixture-of-experts feed-forward
+    "lia_embed_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "lia_ln_add_norm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_float, c_void_p]),
+    "lia_ln_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_gated_act": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "lia_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "lia_moe_tile_rows": (c_int, []),
+    "lia_moe_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lia_moe_gemm": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "lia_moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "lia_conv_prep": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]),
+    "lia_conv_state_update": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                      c_void_p]),
+    "lia_linear_scan": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "lia_kv_store": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int,
+                             c_int, c_int, c_float, c_int, c_void_p]),
+    "lia_window_attn": (c_int, [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]),
 }
 
 EXPORTS = tuple(_PROTOTYPES)

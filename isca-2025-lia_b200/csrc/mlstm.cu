@@ -237,10 +237,11 @@ __global__ void __launch_bounds__(NW * 32, 2) mlstm_scan_kernel(const T* __restr
   if (colb == 0 && threadIdx.x == 0) mst[(size_t)slot * H + h] = m;
 }
 
-// out[row][h][c] = o / sqrt(mean_c(o^2) + eps) * w[h*vdim + c] * sigmoid(gate[row][h*vdim + c]); one warp per (row, head)
+// out[row][h][c] = o / sqrt(mean_c(o^2) + eps) * w[h*vdim + c] * act(gate[row][h*vdim + c]), act = sigmoid (gate_silu == 0) or
+// SiLU; one warp per (row, head)
 template <typename T>
 __global__ void __launch_bounds__(128) headnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, const T* __restrict__ gate, int ldg,
-                                                            T* __restrict__ out, int M, int H, int vdim, float eps) {
+                                                            T* __restrict__ out, int M, int H, int vdim, float eps, int gate_silu) {
   const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (pair >= M * H) return;
   const int row = pair / H, h = pair - row * H;
@@ -251,7 +252,8 @@ __global__ void __launch_bounds__(128) headnorm_gate_kernel(const float* __restr
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
   for (int c = lane; c < vdim; c += 32) {
     const float g = ldf(gate + (size_t)row * ldg + h * vdim + c);
-    stf(out + (size_t)row * H * vdim + h * vdim + c, orow[c] * inv * w[h * vdim + c] * (1.0f / (1.0f + expf(-g))));
+    const float sg = 1.0f / (1.0f + expf(-g));
+    stf(out + (size_t)row * H * vdim + h * vdim + c, orow[c] * inv * w[h * vdim + c] * (gate_silu ? g * sg : sg));
   }
 }
 
@@ -300,13 +302,13 @@ extern "C" int lia_mlstm_scan(const void* q, const void* k, const void* v, int a
 }
 
 extern "C" int lia_headnorm_gate(const float* o, const float* w, const void* gate, int ldg, void* out, int act_f32, int M, int H, int vdim,
-                                 float eps, lia_stream_t stream_) {
+                                 float eps, int gate_silu, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(o && w && gate && out && M > 0 && H > 0 && vdim > 0 && ldg >= H * vdim, "lia_headnorm_gate: bad arguments");
   const long long pairs = (long long)M * H;
   const unsigned grid = (unsigned)((pairs + 3) / 4);
-  if (act_f32) headnorm_gate_kernel<float><<<grid, 128, 0, stream>>>(o, w, reinterpret_cast<const float*>(gate), ldg, reinterpret_cast<float*>(out), M, H, vdim, eps);
-  else headnorm_gate_kernel<bf16><<<grid, 128, 0, stream>>>(o, w, reinterpret_cast<const bf16*>(gate), ldg, reinterpret_cast<bf16*>(out), M, H, vdim, eps);
+  if (act_f32) headnorm_gate_kernel<float><<<grid, 128, 0, stream>>>(o, w, reinterpret_cast<const float*>(gate), ldg, reinterpret_cast<float*>(out), M, H, vdim, eps, gate_silu);
+  else headnorm_gate_kernel<bf16><<<grid, 128, 0, stream>>>(o, w, reinterpret_cast<const bf16*>(gate), ldg, reinterpret_cast<bf16*>(out), M, H, vdim, eps, gate_silu);
   LIA_LAUNCH_CHECK();
   return LIA_OK;
 }

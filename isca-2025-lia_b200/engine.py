@@ -12,8 +12,8 @@ A pass in which every request brings ONE token (a decode step) is launch-bound w
 a few microseconds each -- so it is captured as a CUDA graph the second time its shape comes up and replayed from then
 on: the ids, portions and positions live in one static device buffer that the pinned copy refreshes before every replay;
 the kernels read slots and positions from it, so one graph serves every step of that shape.  "Shape" is the number of
-rows, whether logits are wanted, and how many key ranges the attention splits a history into (``ops.latent_attn_splits``
--- the only launch parameter that depends on the history's length).  The graph replays the very kernels of the eager pass;
+rows, whether logits are wanted, and the model's ``graph_class(longest history)``: whatever else its launches depend on
+(Davasun: how many key ranges the attention splits a history into, ``ops.latent_attn_splits``; Bebulorn: nothing).  The graph replays the very kernels of the eager pass;
 results are bit-identical.
 
 The reference serves one static batch per generate() call (greedy_search.py:37-460); this is the request-level face the
@@ -103,7 +103,7 @@ class Engine:
         n = len(group)
         if not self.graphs or any(len(toks) != 1 for _, toks, _ in group) or len(want) not in (0, n):
             return None
-        return (n, len(want), ops.latent_attn_split_class(max(s[1] + s[3] for s in segs)))
+        return (n, len(want), self.model.graph_class(max(s[1] + s[3] for s in segs)))
 
     def _run_graphed(self, key, ids, segs, meta, want):
         g = self._step_graphs.get(key)

@@ -219,6 +219,11 @@ class DavasunForCausalLM:
         ops.linear_plain(hn, self.head.weight, logits, scale=cfg.logit_scale)
         return logits
 
+    def graph_class(self, max_ctx):
+        """What a decode pass's launches depend on besides the contents of the static buffers: the number of key ranges the
+        attention splits the longest history into."""
+        return ops.latent_attn_split_class(max_ctx)
+
     def generate(self, input_ids, max_new_tokens=32, chunk=None, **unused):
         """Greedy generation of a batch of prompts through the step engine; returns ids [B, S + new] on the input's device."""
         from .engine import Engine

@@ -409,14 +409,14 @@ def mlstm_scan(q, k, v, gates, state_S, state_n, state_m, segs, H, dim, vdim, q_
     return o
 
 
-def headnorm_gate(o, w, gate, out, H, vdim, eps):
-    """out = o / rms_per_head(o) * w * sigmoid(gate)."""
+def headnorm_gate(o, w, gate, out, H, vdim, eps, gate_silu=False):
+    """out = o / rms_per_head(o) * w * sigmoid(gate) (``gate_silu``: * silu(gate))."""
     _req(o, "o", F32); _req(w, "w", F32)
     ldg = _rowmajor(gate, "gate")
     M = o.shape[0]
     if not out.is_contiguous() or tuple(out.shape) != (M, H * vdim) or out.dtype != gate.dtype:
         raise _lib.LiaError("headnorm_gate: out must be a contiguous [M, H*vdim] tensor of the gate's dtype")
-    check(_lib.load().lia_headnorm_gate(_p(o), _p(w), _p(gate), ldg, _p(out), _f32(out), M, H, vdim, float(eps), _stream()),
+    check(_lib.load().lia_headnorm_gate(_p(o), _p(w), _p(gate), ldg, _p(out), _f32(out), M, H, vdim, float(eps), int(gate_silu), _stream()),
           "lia_headnorm_gate")
     count_launches()
     return out
@@ -463,4 +463,187 @@ def latent_attn(qa, cache, meta, gate, out, H, kv_rank, rot, scale, max_ctx=0):
     check(_lib.load().lia_latent_attn(_p(qa), _p(cache), _f32(cache), cache.stride(0), _p(meta), _p(gate), _p(out), _p(ws), nsplit, M, H,
                                       kv_rank, rot, float(scale), _stream()), "lia_latent_attn")
     count_launches(2 if nsplit > 1 else 1)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Models whose sublayers sit between layer norms on a 32-bit residual stream: decay / delta-rule recurrences, sliding-window
+# attention with grouped key/value heads, dense and mixture-of-experts feed-forwards.  (Not in the reference either.)
+# ------------------------------------------------------------------------------------------------------------------
+ACT_NONE, ACT_RELU, ACT_SILU, ACT_GELU_ERF, ACT_GELU_TANH = 0, 1, 2, 3, 4
+I32 = torch.int32
+
+
+def embed_rows(ids, table, x, x_copy=None):
+    """x[r] = table[ids[r]] in fp32; ``x_copy`` receives the same rows (the copy a looped block adds back before a repeat)."""
+    _req(ids, "ids", torch.int64); _req(x, "x", F32); _dev(table, "table")
+    rows, W = x.shape
+    if x_copy is not None:
+        _req(x_copy, "x_copy", F32)
+    check(_lib.load().lia_embed_rows(_p(ids), _p(table), _f32(table), _p(x), _p(x_copy), rows, W, table.shape[0], _stream()), "lia_embed_rows")
+    count_launches()
+    return x
+
+
+def ln_add_norm(x, y, post, mult, pre, h, eps, extra=None):
+    """x += mult * LN(y; post) when y is given, x += extra when given, then h = LN(x; pre) when h is given.  ``post`` and
+    ``pre`` are (weight, bias) pairs of fp32 vectors; x is the fp32 residual stream, updated in place."""
+    _req(x, "x", F32)
+    rows, W = x.shape
+    for t, n in ((y, "y"), (h, "h"), (extra, "extra")):
+        if t is not None and not (t.is_cuda and t.is_contiguous() and tuple(t.shape) == (rows, W)):
+            raise _lib.LiaError(f"ln_add_norm: {n} must be a contiguous CUDA [{rows}, {W}] tensor")
+    for pair, n in ((post, "post"), (pre, "pre")):
+        if pair is not None and not all(t.dtype == F32 and t.numel() == W and t.is_cuda for t in pair):
+            raise _lib.LiaError(f"ln_add_norm: {n} must be a (weight, bias) pair of fp32 [{W}] vectors")
+    if extra is not None:
+        _req(extra, "extra", F32)
+    wp, bp = post if post is not None else (None, None)
+    wn, bn = pre if pre is not None else (None, None)
+    check(_lib.load().lia_ln_add_norm(_p(x), _p(y), _f32(y) if y is not None else 0, _p(wp), _p(bp), float(mult), _p(extra), _p(wn), _p(bn),
+                                      _p(h), _f32(h) if h is not None else 0, rows, W, float(eps), _stream()), "lia_ln_add_norm")
+    count_launches()
+    return x
+
+
+def ln_gather(x, rows, norm, h, eps):
+    """h[r] = LN(x[rows[r]]; norm): the final norm of the rows whose logits are wanted."""
+    _req(x, "x", F32); _req(rows, "rows", I32)
+    n, W = h.shape
+    w, b = norm
+    if rows.numel() != n or x.shape[1] != W or not h.is_contiguous() or w.numel() != W or b.numel() != W:
+        raise _lib.LiaError("ln_gather: shapes do not agree")
+    check(_lib.load().lia_ln_gather(_p(x), _p(rows), _p(_req(w, "w", F32)), _p(_req(b, "b", F32)), _p(h), _f32(h), n, W, float(eps), _stream()),
+          "lia_ln_gather")
+    count_launches()
+    return h
+
+
+def gated_act(inp, F, out, act, up_off=-1):
+    """out = act(inp[:, :F]) * inp[:, up_off:up_off + F] (``up_off`` < 0: no second factor)."""
+    ld = _rowmajor(inp, "inp")
+    M = inp.shape[0]
+    if tuple(out.shape) != (M, F) or not out.is_contiguous() or out.dtype != inp.dtype:
+        raise _lib.LiaError("gated_act: out must be a contiguous [M, F] tensor of the input's dtype")
+    check(_lib.load().lia_gated_act(_p(inp), ld, up_off, _p(out), _f32(out), M, F, act, _stream()), "lia_gated_act")
+    count_launches()
+    return out
+
+
+def router_topk(logits, top, idx, wt):
+    """Softmax over the experts, the ``top`` largest scores and their renormalised weights: idx int32 [M, top], wt fp32."""
+    _req(logits, "logits", F32); _req(idx, "idx", I32); _req(wt, "wt", F32)
+    M, E = logits.shape
+    if tuple(idx.shape) != (M, top) or tuple(wt.shape) != (M, top):
+        raise _lib.LiaError("router_topk: idx and wt must be [M, top]")
+    check(_lib.load().lia_router_topk(_p(logits), _p(idx), _p(wt), M, E, top, _stream()), "lia_router_topk")
+    count_launches()
+
+
+def moe_tiles(pairs, E):
+    """Row tiles that always hold ``pairs`` (token, choice) pairs grouped by expert."""
+    tm = _lib.load().lia_moe_tile_rows()
+    return (pairs + min(E, pairs) * (tm - 1)) // tm, tm
+
+
+def moe_plan(idx, E, perm, tile_expert, pos_of):
+    _req(idx, "idx", I32); _req(perm, "perm", I32); _req(tile_expert, "tile_expert", I32); _req(pos_of, "pos_of", I32)
+    check(_lib.load().lia_moe_plan(_p(idx), idx.numel(), E, tile_expert.numel(), _p(perm), _p(tile_expert), _p(pos_of), _stream()), "lia_moe_plan")
+    count_launches()
+
+
+def moe_gemm(a, w, out, idx, wt, top, up, act=ACT_NONE, perm=None, tile_expert=None):
+    """One projection of every expert over its own rows; ``w`` [E, N, K].  up: out[place] = act(a[token] @ w[e].T);
+    down: out[pair] = wt[pair] * a[place] @ w[e].T (fp32).  Without a plan (``perm`` None) a pair's place is the pair."""
+    _dev(a, "a"); _dev(w, "w"); _dev(out, "out")
+    E, N, K = w.shape
+    if not (w.is_contiguous() and a.is_contiguous() and out.is_contiguous() and a.shape[1] == K and out.shape[1] == N):
+        raise _lib.LiaError(f"moe_gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    check(_lib.load().lia_moe_gemm(_p(a), _f32(a), K, _p(w), _f32(w), N * K, _p(out), _f32(out), N, _p(perm), _p(tile_expert),
+                                   tile_expert.numel() if tile_expert is not None else 0, _p(idx), _p(wt), idx.numel(), top, N, K, int(up), act,
+                                   _stream()), "lia_moe_gemm")
+    count_launches()
+    return out
+
+
+def moe_combine(ypair, shared, y, top):
+    _req(ypair, "ypair", F32); _req(y, "y", F32)
+    M, W = y.shape
+    if shared is not None and not (shared.is_contiguous() and tuple(shared.shape) == (M, W)):
+        raise _lib.LiaError("moe_combine: the shared expert's output must be a contiguous [M, W] tensor")
+    check(_lib.load().lia_moe_combine(_p(ypair), _p(shared), _f32(shared) if shared is not None else 1, _p(y), M, W, top, _stream()),
+          "lia_moe_combine")
+    count_launches()
+    return y
+
+
+def conv_prep(y, offs, wconv, conv_state, meta, gates, a_log, dt_bias, qk, v, G, H, dim, vdim, taps, q_scale, unit_eps=1e-6):
+    """Short convolution + SiLU of the q | k | v columns of ``y`` (column offsets ``offs``), unit q and k per head, and the
+    gates beta | g in place of the raw gate projections in ``gates`` [M, 2H]."""
+    ld = _rowmajor(y, "y")
+    for t, n in ((wconv, "wconv"), (conv_state, "conv_state"), (gates, "gates"), (a_log, "a_log"), (dt_bias, "dt_bias"), (qk, "qk"), (v, "v")):
+        _req(t, n, F32)
+    _req(meta, "meta", I32)
+    M, C = y.shape[0], 2 * G * dim + H * vdim
+    if tuple(wconv.shape) != (C, taps) or tuple(conv_state.shape[1:]) != (max(taps - 1, 1), C) or tuple(gates.shape) != (M, 2 * H) \
+            or tuple(qk.shape) != (M, 2 * G * dim) or tuple(v.shape) != (M, H * vdim):
+        raise _lib.LiaError("conv_prep: shapes do not agree")
+    check(_lib.load().lia_conv_prep(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], _p(wconv), _p(conv_state), _p(meta), _p(gates), _p(a_log),
+                                    _p(dt_bias), _p(qk), _p(v), M, G, H, dim, vdim, taps, float(q_scale), float(unit_eps), _stream()), "lia_conv_prep")
+    count_launches()
+
+
+def conv_state_update(y, offs, nqk, nv, conv_state, segs, taps):
+    """The last ``taps`` - 1 inputs of every portion become its sequence's convolution state (after ``conv_prep``)."""
+    ld = _rowmajor(y, "y")
+    _req(conv_state, "conv_state", F32); _req(segs, "segs", I32)
+    if taps > 1:
+        check(_lib.load().lia_conv_state_update(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], nqk, nv, _p(conv_state), _p(segs), segs.shape[0],
+                                                taps, _stream()), "lia_conv_state_update")
+        count_launches()
+
+
+def linear_scan(q, k, v, state_S, segs, H, G, dim, vdim, o, decay=None, gates=None, in_silu=False):
+    """Matrix-state recurrence over every portion of the step (csrc/linear_scan.cu): with ``decay`` [H] the fixed-decay form,
+    with ``gates`` [rows, 2H] = beta | g the gated delta rule.  q, k: column slices with one row stride, G heads."""
+    ld = _rowmajor(q, "q")
+    if _rowmajor(k, "k") != ld or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise _lib.LiaError("linear_scan: q and k must be slices of one buffer, v of the same type")
+    ldv = _rowmajor(v, "v")
+    _req(state_S, "state_S", F32); _req(segs, "segs", I32); _req(o, "o", F32)
+    if (decay is None) == (gates is None):
+        raise _lib.LiaError("linear_scan: give either decay or gates")
+    M = q.shape[0]
+    if tuple(o.shape) != (M, H * vdim) or tuple(state_S.shape[1:]) != (H, vdim, dim) or (gates is not None and tuple(gates.shape) != (M, 2 * H)) \
+            or (decay is not None and decay.numel() != H):
+        raise _lib.LiaError("linear_scan: shapes do not agree")
+    check(_lib.load().lia_linear_scan(_p(q), _p(k), ld, _p(v), ldv, _f32(q), int(in_silu), _p(_req(decay, "decay", F32) if decay is not None else None),
+                                      _p(_req(gates, "gates", F32) if gates is not None else None), _p(state_S), _p(segs), segs.shape[0], H, G, dim,
+                                      vdim, _p(o), _stream()), "lia_linear_scan")
+    count_launches()
+    return o
+
+
+def kv_store(k, v, meta, kcache, vcache, G, dim, vdim, eps, norm_values=True):
+    """Keys as they are, values divided by their per-head root mean square, into the caches at every row's (slot, position)."""
+    ldk, ldv = _rowmajor(k, "k"), _rowmajor(v, "v")
+    _req(meta, "meta", I32)
+    if not (kcache.dtype == vcache.dtype == k.dtype == v.dtype and kcache.is_contiguous() and vcache.is_contiguous()
+            and kcache.shape[2] == G * dim and vcache.shape[2] == G * vdim):
+        raise _lib.LiaError("kv_store: caches must be contiguous [slots, capacity, G * dim | G * vdim] tensors of the activations' dtype")
+    check(_lib.load().lia_kv_store(_p(k), ldk, _p(v), ldv, _f32(k), _p(meta), _p(kcache), kcache.stride(0), _p(vcache), vcache.stride(0), k.shape[0],
+                                   G, dim, vdim, float(eps), int(norm_values), _stream()), "lia_kv_store")
+    count_launches()
+
+
+def window_attn(q, kcache, vcache, meta, temp, out, H, G, dim, vdim, window, scale, softcap):
+    """Softmax attention of every row over the last ``window`` cached positions of its sequence (csrc/window_attn.cu)."""
+    ldq = _rowmajor(q, "q")
+    _req(meta, "meta", I32); _req(temp, "temp", F32)
+    M = q.shape[0]
+    if not (out.is_contiguous() and tuple(out.shape) == (M, H * vdim) and out.dtype == q.dtype == kcache.dtype == vcache.dtype and temp.numel() == H):
+        raise _lib.LiaError("window_attn: out must be a contiguous [M, H * vdim] tensor of the activations' dtype, temp [H]")
+    check(_lib.load().lia_window_attn(_p(q), ldq, _f32(q), _p(kcache), kcache.stride(0), _p(vcache), vcache.stride(0), _p(meta), _p(temp), _p(out),
+                                      M, H, G, dim, vdim, int(window), float(scale), float(softcap), _stream()), "lia_window_attn")
+    count_launches()
     return out

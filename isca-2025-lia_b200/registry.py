@@ -22,10 +22,17 @@ def _davasun():
     return DavasunForCausalLM
 
 
+def _bebulorn():
+    from .modeling_bebulorn import BebulornForCausalLM
+    return BebulornForCausalLM
+
+
 register("OPTForCausalLM", _opt)
 register("opt", _opt)
 register("Davasun", _davasun)
 register("DavasunForCausalLM", _davasun)
+register("Bebulorn", _bebulorn)
+register("BebulornForCausalLM", _bebulorn)
 
 
 def architecture_of(path):

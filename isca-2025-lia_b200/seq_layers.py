@@ -1,6 +1,8 @@
 """Sequence mixers and feed-forwards that run on a 32-bit residual stream, each with its constants as parameters so that
 any model design can assemble them: a matrix-memory recurrent mixer (mLSTM), attention over a latent key/value cache with
-a partly rotated query/key and an output gate, and a clamped gated feed-forward.  Each object owns its (fused) weights,
+a partly rotated query/key and an output gate, linear attention with a fixed decay per head, the gated delta rule behind a
+short convolution, sliding-window attention with grouped key/value heads, and the feed-forwards -- clamped gated, plain
+gated with any activation, and a routed mixture of experts with a shared expert.  Each object owns its (fused) weights,
 registers its per-sequence state with a ``seq_state.SlotState`` and runs one step over a batch of portions
 (``StepBatch``) through the kernels of ``ops``.
 
@@ -168,3 +170,179 @@ class ClampedGLU:
         y = torch.empty(h.shape[0], self.ff, dtype=self.dtype, device=h.device)
         ops.clamped_glu(gu, self.gate_up.offsets[1], self.ff, y, self.limit, self.alpha)
         return self.down(y)
+
+
+class DecayLinearAttentionMixer:
+    """Linear attention with a fixed decay per head ("lightning" attention): q, k, v = act(Wq h), act(Wk h), act(Wv h);
+    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (csrc/linear_scan.cu, which applies ``act`` = SiLU as it reads the
+    projection); the concatenated heads RMS-normed together with a per-channel weight, times sigmoid(Wg h), then Wo."""
+
+    def __init__(self, w, heads, dim, vdim, decay, norm_eps, dtype, device):
+        if len(decay) != heads:
+            raise ValueError(f"{len(decay)} decays for {heads} heads")
+        self.H, self.dim, self.vdim, self.eps, self.dtype = heads, dim, vdim, float(norm_eps), dtype
+        self.proj = Linear([w["q"], w["k"], w["v"], w["g"]], dtype, device)
+        self.decay = torch.tensor([float(d) for d in decay], dtype=torch.float64).to(device=device, dtype=F32)
+        self.norm_w = w["norm"].to(device=device, dtype=F32).contiguous()
+        self.out = Linear([w["o"]], dtype, device)
+
+    def new_state(self, slots):
+        return (slots.add_recurrent((self.H, self.vdim, self.dim)),)
+
+    def __call__(self, h, batch, state):
+        (S,) = state
+        M, H = h.shape[0], self.H
+        y = self.proj(h)
+        q, k, v, g = (self.proj.part(y, i) for i in range(4))
+        o = torch.empty(M, H * self.vdim, dtype=F32, device=h.device)
+        ops.linear_scan(q, k, v, S, batch.segs, H, H, self.dim, self.vdim, o, decay=self.decay, in_silu=True)
+        on = torch.empty(M, H * self.vdim, dtype=self.dtype, device=h.device)
+        ops.headnorm_gate(o, self.norm_w, g, on, 1, H * self.vdim, self.eps)       # one norm over all heads
+        return self.out(on)
+
+
+class DeltaRuleMixer:
+    """Gated delta rule.  q, k (kv_heads x dim) and v (heads x vdim) pass a short causal convolution per channel and SiLU; q, k
+    become unit vectors per head (q times dim^-1/2); per head beta = sigmoid(Wb h) and g = exp(-exp(A_log) softplus(Wa h + dt_bias));
+    S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; each head's o RMS-normed with a weight shared by the heads, times
+    silu(Wg h); then Wo.  Per-sequence state: S and the last taps - 1 inputs of the convolution."""
+
+    def __init__(self, w, heads, kv_heads, dim, vdim, taps, norm_eps, dtype, device, unit_eps=1e-6):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads do not divide into {kv_heads} query/key heads")
+        self.H, self.G, self.dim, self.vdim, self.taps = heads, kv_heads, dim, vdim, int(taps)
+        self.eps, self.unit_eps, self.dtype = float(norm_eps), float(unit_eps), dtype
+        self.proj = Linear([w["q"], w["k"], w["v"], w["g"]], dtype, device)
+        self.w_gates = torch.cat([w["b"], w["a"]], 0).to(device=device, dtype=dtype).contiguous()        # -> beta | decay inputs
+        self.w_conv = torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]], 0).to(device=device, dtype=F32).contiguous()
+        self.a_log = w["A_log"].to(device=device, dtype=F32).contiguous()
+        self.dt_bias = w["dt_bias"].to(device=device, dtype=F32).contiguous()
+        self.norm_w = w["norm"].to(device=device, dtype=F32).repeat(heads).contiguous()
+        self.out = Linear([w["o"]], dtype, device)
+        self.channels = 2 * kv_heads * dim + heads * vdim
+
+    def new_state(self, slots):
+        return (slots.add_recurrent((self.H, self.vdim, self.dim)), slots.add_recurrent((max(self.taps - 1, 1), self.channels)))
+
+    def __call__(self, h, batch, state):
+        S, conv = state
+        M, H, G = h.shape[0], self.H, self.G
+        y = self.proj(h)
+        gates = torch.empty(M, 2 * H, dtype=F32, device=h.device)
+        ops.linear_small(h, self.w_gates, None, gates, ops.GATE_NONE)
+        qk = torch.empty(M, 2 * G * self.dim, dtype=F32, device=h.device)
+        v = torch.empty(M, H * self.vdim, dtype=F32, device=h.device)
+        offs = self.proj.offsets[:3]
+        ops.conv_prep(y, offs, self.w_conv, conv, batch.meta, gates, self.a_log, self.dt_bias, qk, v, G, H, self.dim, self.vdim, self.taps,
+                      float(self.dim) ** -0.5, self.unit_eps)
+        ops.conv_state_update(y, offs, G * self.dim, H * self.vdim, conv, batch.segs, self.taps)
+        o = torch.empty(M, H * self.vdim, dtype=F32, device=h.device)
+        ops.linear_scan(qk[:, :G * self.dim], qk[:, G * self.dim:], v, S, batch.segs, H, G, self.dim, self.vdim, o, gates=gates)
+        on = torch.empty(M, H * self.vdim, dtype=self.dtype, device=h.device)
+        ops.headnorm_gate(o, self.norm_w, self.proj.part(y, 3), on, H, self.vdim, self.eps, gate_silu=True)
+        return self.out(on)
+
+
+class WindowAttentionMixer:
+    """Softmax attention over the last ``window`` positions, ``kv_heads`` key/value heads shared by groups of query heads, no
+    positional rotation.  Values are divided by their per-head root mean square before they are cached; a score is
+    (q . k) * scale * temp_h, then softcap * tanh(score / softcap) (csrc/window_attn.cu); output Wo on the concatenated heads."""
+
+    def __init__(self, w, heads, kv_heads, dim, vdim, window, scale, softcap, norm_eps, dtype, device, norm_values=True):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads do not divide into {kv_heads} key/value heads")
+        self.H, self.G, self.dim, self.vdim, self.window = heads, kv_heads, dim, vdim, int(window)
+        self.scale, self.softcap, self.eps, self.dtype, self.norm_values = float(scale), float(softcap), float(norm_eps), dtype, norm_values
+        self.proj = Linear([w["q"], w["k"], w["v"]], dtype, device)
+        temp = w.get("temp")
+        self.temp = (temp if temp is not None else torch.ones(heads)).to(device=device, dtype=F32).contiguous()
+        self.out = Linear([w["o"]], dtype, device)
+
+    def new_state(self, slots):
+        return (slots.add_rows(self.G * self.dim, self.dtype), slots.add_rows(self.G * self.vdim, self.dtype))
+
+    def __call__(self, h, batch, state):
+        kc, vc = state
+        M = h.shape[0]
+        y = self.proj(h)
+        q, k, v = (self.proj.part(y, i) for i in range(3))
+        ops.kv_store(k, v, batch.meta, kc, vc, self.G, self.dim, self.vdim, self.eps, self.norm_values)
+        o = torch.empty(M, self.H * self.vdim, dtype=self.dtype, device=h.device)
+        ops.window_attn(q, kc, vc, batch.meta, self.temp, o, self.H, self.G, self.dim, self.vdim, self.window, self.scale, self.softcap)
+        return self.out(o)
+
+
+class GatedMLP:
+    """Dense gated feed-forward: Wdown (act(Wgate h) * (Wup h))."""
+
+    def __init__(self, w, ff, act, dtype, device):
+        self.ff, self.act, self.dtype = ff, act, dtype
+        self.gate_up = Linear([w["gate"], w["up"]], dtype, device)
+        self.down = Linear([w["down"]], dtype, device)
+
+    def __call__(self, h):
+        gu = self.gate_up(h)
+        y = torch.empty(h.shape[0], self.ff, dtype=self.dtype, device=h.device)
+        ops.gated_act(gu, self.ff, y, self.act, up_off=self.gate_up.offsets[1])
+        return self.down(y)
+
+
+class PlainMLP:
+    """Wdown act(Wup h)."""
+
+    def __init__(self, w, ff, act, dtype, device):
+        self.ff, self.act, self.dtype = ff, act, dtype
+        self.up = Linear([w["up"]], dtype, device)
+        self.down = Linear([w["down"]], dtype, device)
+
+    def __call__(self, h):
+        u = self.up(h)
+        y = torch.empty(h.shape[0], self.ff, dtype=self.dtype, device=h.device)
+        ops.gated_act(u, self.ff, y, self.act)
+        return self.down(y)
+
+
+class MoEFeedForward:
+    """Routed mixture of experts: router logits in fp32, softmax over all experts, the ``top`` largest scores renormalised
+    (divided by their sum + 1e-20); every expert is Wdown act(Wup h); a shared expert (optional) runs for every token and is
+    added.  ``experts_w``: list of {"up", "down"} per expert.  The (token, choice) pairs are grouped by expert on the device
+    (no host round trip) and each projection runs as one grouped launch; a handful of pairs (decoding) take the form with one
+    warp per output instead.  The result is fp32."""
+
+    FEW_PAIRS = 48
+
+    def __init__(self, router_w, experts_w, top, ff, act, shared, dtype, device):
+        self.E, self.top, self.ff, self.act, self.dtype = len(experts_w), int(top), ff, act, dtype
+        if not 1 <= self.top <= self.E:
+            raise ValueError(f"top = {top} of {self.E} experts")
+        self.router = router_w.to(device=device, dtype=dtype).contiguous()
+        self.w_up = torch.stack([e["up"] for e in experts_w]).to(device=device, dtype=dtype).contiguous()         # [E, ff, W]
+        self.w_down = torch.stack([e["down"] for e in experts_w]).to(device=device, dtype=dtype).contiguous()     # [E, W, ff]
+        self.shared = shared
+
+    def __call__(self, h):
+        M, W, dev = h.shape[0], h.shape[1], h.device
+        E, top = self.E, self.top
+        logits = torch.empty(M, E, dtype=F32, device=dev)
+        ops.linear_small(h, self.router, None, logits, ops.GATE_NONE)
+        idx = torch.empty(M, top, dtype=torch.int32, device=dev)
+        wt = torch.empty(M, top, dtype=F32, device=dev)
+        ops.router_topk(logits, top, idx, wt)
+        pairs = M * top
+        ypair = torch.empty(pairs, W, dtype=F32, device=dev)
+        if pairs <= self.FEW_PAIRS:
+            mid = torch.empty(pairs, self.ff, dtype=self.dtype, device=dev)
+            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act)
+            ops.moe_gemm(mid, self.w_down, ypair, idx, wt, top, False)
+        else:
+            n_tiles, tm = ops.moe_tiles(pairs, E)
+            perm = torch.empty(n_tiles * tm, dtype=torch.int32, device=dev)
+            tile_expert = torch.empty(n_tiles, dtype=torch.int32, device=dev)
+            pos_of = torch.empty(pairs, dtype=torch.int32, device=dev)
+            ops.moe_plan(idx, E, perm, tile_expert, pos_of)
+            mid = torch.empty(n_tiles * tm, self.ff, dtype=self.dtype, device=dev)
+            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, perm, tile_expert)
+            ops.moe_gemm(mid, self.w_down, ypair, idx, wt, top, False, ops.ACT_NONE, perm, tile_expert)
+        y = torch.empty(M, W, dtype=F32, device=dev)
+        ops.moe_combine(ypair, self.shared(h) if self.shared is not None else None, y, top)
+        return y
