@@ -91,6 +91,10 @@ class _Recorder:
         self.calls.append((ids.tolist(), batch.segs.tolist(), batch.meta.tolist(), None if want is None else want.tolist()))
         return None if want is None else torch.zeros(want.numel(), 50)
 
+    def graph_class(self, max_ctx):
+        from lia_b200 import ops
+        return ops.latent_attn_split_class(max_ctx)
+
 
 def test_engine_lays_out_entries_and_cuts_passes():
     m = _Recorder()
