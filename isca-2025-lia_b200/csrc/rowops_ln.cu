@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
     __syncwarp();
   }
   __syncwarp();
-  if (lane < top) wt[(size_t)row * top + lane] = wt[(size_t)row * top + lane] / (chosen_sum + 1e-20f);
+  for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = wt[(size_t)row * top + t] / (chosen_sum + 1e-20f);
 }
 
 // ---------------------------------------------------------------------------------------------------- experts
@@ -407,7 +407,7 @@ extern "C" int lia_gated_act(const void* in, int ld, int up_off, void* out, int 
 
 extern "C" int lia_router_topk(const float* logits, int* idx, float* wt, int M, int E, int top, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  LIA_CHECK_ARG(logits && idx && wt && M > 0 && E > 0 && top > 0 && top <= E && top <= 32 && E <= 2048, "lia_router_topk: bad arguments (E=%d top=%d)", E, top);
+  LIA_CHECK_ARG(logits && idx && wt && M > 0 && E > 0 && top > 0 && top <= E && E <= 2048, "lia_router_topk: bad arguments (E=%d top=%d)", E, top);
   router_topk_kernel<<<(M + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, idx, wt, M, E, top);
   LIA_LAUNCH_CHECK();
   return LIA_OK;

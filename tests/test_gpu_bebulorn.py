@@ -489,11 +489,11 @@ def test_freed_slots_are_reused_clean_and_passes_cut_long_entries():
 
 @pytest.mark.parametrize("window", [7, 32, 45])
 def test_window_edge_through_the_model_in_prompts_and_in_decoding(window):
-    """One sharp attention layer (large scale, no effective cap): changing the token that sits just inside the window of the
-    last position changes its logits, changing the one just outside does not -- in a whole prompt and when the last tokens
-    are decoded one by one, with the edge falling inside a prompt portion or among the decoded tokens."""
-    cfg = config([attention(2, 1, 16, 16, window, scale=4.0, softcap=1000.0)], vocab=50, width=32, eps=1e-5)
-    _, w, m = build(cfg, F32, seed=12, std_scale=2.0)
+    """One attention layer with flat weights (every key of the window counts): changing the token that sits just inside the
+    window of the last position changes its logits, changing the one just outside does not -- in a whole prompt and when the
+    last tokens are decoded one by one, with the edge falling inside a prompt portion or among the decoded tokens."""
+    cfg = config([attention(2, 1, 16, 16, window, scale=0.5, softcap=1000.0)], vocab=50, width=32, eps=1e-5)
+    _, w, m = build(cfg, F32, seed=12)
     n = 100
     toks = toks_for(cfg, n, 10)
     inside, outside = n - window, n - window - 1
