@@ -1,5 +1,7 @@
 """`bench.py --compare-davasun`: prefill and decode throughput of Davasun at layer sizes of a real model (random weights)
 beside OPT -- the closest existing model -- at equal width and depth, with every kernel's time against its roofline.
+`bench.py --compare-bebulorn`: the same for Bebulorn beside Davasun, the closest existing model (step-served, recurrent and
+attention mixers on a 32-bit residual stream).
 
 Each operation of ``ops`` is wrapped for the duration of an instrumented pass: CUDA events around the call, and the
 operation's algorithmic FLOPs and bytes from its arguments.  roofline time = max(FLOPs / peak, bytes / HBM bandwidth)
@@ -45,6 +47,22 @@ def _cost(name, a, kw):
         qa, cache, meta, out, H, rank, rot = a[0], a[1], a[2], a[4], a[5], a[6], a[7]
         keys = float(kw.get("_keys", 0))                                           # sum over rows of visible keys
         return 2.0 * keys * H * (2 * rank + rot), _nbytes(qa, out) + kw.get("_ctx", 0) * (rank + rot) * cache.element_size(), "f32"
+    if name == "linear_scan":
+        q, S, segs, H, G, dim, vdim, o = a[0], a[3], a[4], a[5], a[6], a[7], a[8], a[9]
+        M = q.shape[0]
+        state = 2.0 * segs.shape[0] * H * dim * vdim * 4
+        per_token = 8.0 if kw.get("gates") is not None else 4.0                    # delta: two dot products and two updates per cell
+        return per_token * M * H * dim * vdim, state + M * (2 * G * dim + H * vdim) * q.element_size() + _nbytes(o), "f32"
+    if name == "window_attn":
+        q, kc, out, H, G, dim, vdim = a[0], a[1], a[5], a[6], a[7], a[8], a[9]
+        keys = float(kw.get("_wkeys", 0))                                          # sum over rows of keys inside the window
+        return 2.0 * keys * H * (dim + vdim), _nbytes(q, out) + kw.get("_wctx", 0) * G * (dim + vdim) * kc.element_size(), "f32"
+    if name == "moe_gemm":
+        x, w, out, idx = a[0], a[1], a[2], a[3]
+        pairs, N, K = idx.numel(), w.shape[1], w.shape[2]
+        touched = min(w.shape[0], pairs)
+        kind = "tc" if x.dtype == BF16 and pairs > 64 else "mem"
+        return 2.0 * pairs * N * K, pairs * (K * x.element_size() + N * out.element_size()) + touched * N * K * w.element_size(), kind
     if name == "attn_prefill":
         q, kc, B, S = a[0], a[1], a[3], a[4]
         H, d = kc.shape[2], kc.shape[3]
@@ -59,7 +77,9 @@ def _cost(name, a, kw):
 
 class Instrument:
     NAMES = ("gemm", "linear_plain", "linear_small", "mlstm_scan", "headnorm_gate", "latent_prep", "latent_attn", "clamped_glu",
-             "rms_add_norm", "embed_rmsnorm", "rms_gather", "layernorm", "attn_prefill", "attn_decode", "embed", "argmax", "argmax_f32")
+             "rms_add_norm", "embed_rmsnorm", "rms_gather", "layernorm", "attn_prefill", "attn_decode", "embed", "argmax", "argmax_f32",
+             "linear_scan", "conv_prep", "conv_state_update", "kv_store", "window_attn", "ln_add_norm", "embed_rows", "ln_gather", "gated_act",
+             "router_topk", "moe_plan", "moe_gemm", "moe_combine")
 
     def __init__(self):
         self.records, self.saved, self.extra = [], {}, {}
@@ -116,6 +136,91 @@ def davasun_config(width, n_layers):
             "norm": {"eps": 1e-6}, "logit_scale": 1.0}
 
 
+def bebulorn_config(width, n_layers):
+    """Layer sizes of a ~1-3 B model: heads of 128 x 128 throughout; delta layers with half as many query/key heads as value
+    heads and a 4-tap convolution; attention with 8 key/value heads and a window of 1024; feed-forwards alternate between a
+    dense 2.75 x one and 16 experts of 0.6875 x (2 chosen) plus a shared expert of the same size.  Order: delta, lightning,
+    lightning, attention."""
+    H = width // 128
+    dense = {"kind": "dense", "ff": width * 11 // 4}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": width * 11 // 16}, "shared": {"ff": width * 11 // 16}}
+    li = lambda mlp: {"type": "lightning", "mlp": mlp,  # noqa: E731
+                      "mixer": {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(1 + 7 * i / max(H - 1, 1)) for i in range(H)]}}
+    de = {"type": "delta", "mixer": {"heads": H, "kv_heads": max(1, H // 2), "dim": 128, "vdim": 128, "conv": 4}, "mlp": dense}
+    at = {"type": "attention", "mlp": moe,
+          "mixer": {"heads": H, "kv_heads": min(8, H), "dim": 128, "vdim": 128, "mask": {"size": 1024}, "scale": 128 ** -0.5, "softcap": 50.0}}
+    pattern = [de, li(moe), li(dense), at]
+    return {"architecture": "Bebulorn", "vocab": 32000, "width": width, "layers": [pattern[i % 4] for i in range(n_layers)],
+            "loop": {"start": 0, "stop": 0, "times": 1}, "norm": {"eps": 1e-6}, "residual_mult": 0.5}
+
+
+def _window_keys(layers, n_new, ctx_before):
+    """Sum over the new rows of the keys inside the first attention layer's window, and the cached rows those windows span."""
+    win = next((l["mixer"]["mask"]["size"] for l in layers if l["type"] == "attention"), 0)
+    if not win:
+        return 0, 0
+    keys = sum(min(win, ctx_before + i + 1) for i in range(n_new))
+    return keys, min(ctx_before + n_new, win + n_new - 1)
+
+
+def step_model(m, cfg, pk, g, prompt, decode_ctx, decode_batches, new):
+    """Prefill and decode numbers of a model served by the step engine, with the per-kernel table of one instrumented pass."""
+    from .engine import Engine
+    toks = torch.randint(0, cfg.vocab, (prompt,), generator=g).tolist()
+    eng = Engine(m, max_tokens=decode_ctx + new + 8, max_requests=max(decode_batches), max_rows=prompt)
+
+    def prefill():
+        eng.step([{"id": "p", "tokens": toks, "want": [prompt - 1]}], end=["p"])
+    ms = _timed(prefill)
+    d = {"prefill_ms": round(ms, 3), "prefill_tokens_per_s": round(prompt / ms * 1e3, 1)}
+    with Instrument() as ins:
+        wk, wc = _window_keys(cfg.layers, prompt, 0)
+        ins.extra = {"_keys": prompt * (prompt + 1) / 2, "_ctx": prompt, "_wkeys": wk, "_wctx": wc}
+        prefill()
+    d["prefill_kernels"] = ins.table(pk)
+    for B in decode_batches:
+        ids = list(range(B))
+        ctx = torch.randint(0, cfg.vocab, (decode_ctx,), generator=g).tolist()
+        for i in ids:
+            eng.step([{"id": i, "tokens": ctx, "want": []}])
+        step = lambda: eng.step([{"id": i, "tokens": [7], "want": [0]} for i in ids])  # noqa: E731
+        ms = _timed(step, warmup=3, iters=new - 4)
+        d[f"decode_b{B}_ms_per_step"] = round(ms, 3)
+        d[f"decode_b{B}_tokens_per_s"] = round(B / ms * 1e3, 1)
+        eng.graphs = False                    # the timed steps above replay a CUDA graph; the per-kernel pass launches eagerly
+        ms = _timed(step, warmup=1, iters=2)
+        d[f"decode_b{B}_ms_per_step_eager"] = round(ms, 3)
+        with Instrument() as ins:
+            wk, wc = _window_keys(cfg.layers, 1, decode_ctx + new)
+            ins.extra = {"_keys": B * (decode_ctx + new), "_ctx": B * (decode_ctx + new), "_wkeys": B * wk, "_wctx": B * wc}
+            step()
+        eng.graphs = True
+        d[f"decode_b{B}_kernels"] = ins.table(pk)
+        eng.step([], end=ids)
+    return d
+
+
+def run_bebulorn(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=2048, decode_batches=(1, 16), new=16):
+    """Bebulorn beside Davasun at equal width and depth."""
+    from .modeling_bebulorn import BebulornConfig, BebulornForCausalLM
+    from .modeling_davasun import DavasunConfig, DavasunForCausalLM
+    dev = torch.device("cuda", 0)
+    props = torch.cuda.get_device_properties(dev)
+    pk = dict(pk, fp32_nominal_tflops=props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12)
+    out = {"peaks": pk, "sizes": []}
+    g = torch.Generator().manual_seed(0)
+    for width in widths:
+        rec = {"width": width, "layers": n_layers, "prompt": prompt, "decode_context": decode_ctx}
+        for name, make in (("bebulorn", lambda: BebulornForCausalLM(BebulornConfig.from_dict(bebulorn_config(width, n_layers)), dev, BF16)),
+                           ("davasun", lambda: DavasunForCausalLM(DavasunConfig.from_dict(davasun_config(width, n_layers)), dev, BF16))):
+            m = make().init_weights(seed=1)
+            rec[name] = step_model(m, m.config, pk, g, prompt, decode_ctx, decode_batches, new)
+            del m
+            torch.cuda.empty_cache()
+        out["sizes"].append(rec)
+    return out
+
+
 def _timed(fn, warmup=3, iters=5):
     for _ in range(warmup):
         fn()
@@ -130,7 +235,6 @@ def _timed(fn, warmup=3, iters=5):
 
 
 def run(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=2048, decode_batches=(1, 16), new=16):
-    from .engine import Engine
     from .modeling_davasun import DavasunConfig, DavasunForCausalLM
     from .modeling_opt import OPTConfig, OPTForCausalLM
     dev = torch.device("cuda", 0)
@@ -143,35 +247,7 @@ def run(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=2048, decod
         # ---------------- Davasun
         cfg = DavasunConfig.from_dict(davasun_config(width, n_layers))
         m = DavasunForCausalLM(cfg, dev, BF16).init_weights(seed=1)
-        toks = torch.randint(0, cfg.vocab, (prompt,), generator=g).tolist()
-        eng = Engine(m, max_tokens=decode_ctx + new + 8, max_requests=max(decode_batches), max_rows=prompt)
-
-        def prefill():
-            eng.step([{"id": "p", "tokens": toks, "want": [prompt - 1]}], end=["p"])
-        ms = _timed(prefill)
-        d = {"prefill_ms": round(ms, 3), "prefill_tokens_per_s": round(prompt / ms * 1e3, 1)}
-        with Instrument() as ins:
-            ins.extra = {"_keys": prompt * (prompt + 1) / 2, "_ctx": prompt}
-            prefill()
-        d["prefill_kernels"] = ins.table(pk)
-        for B in decode_batches:
-            ids = list(range(B))
-            ctx = torch.randint(0, cfg.vocab, (decode_ctx,), generator=g).tolist()
-            for i in ids:
-                eng.step([{"id": i, "tokens": ctx, "want": []}])
-            step = lambda: eng.step([{"id": i, "tokens": [7], "want": [0]} for i in ids])  # noqa: E731
-            ms = _timed(step, warmup=3, iters=new - 4)
-            d[f"decode_b{B}_ms_per_step"] = round(ms, 3)
-            d[f"decode_b{B}_tokens_per_s"] = round(B / ms * 1e3, 1)
-            eng.graphs = False                    # the timed steps above replay a CUDA graph; the per-kernel pass launches eagerly
-            ms = _timed(step, warmup=1, iters=2)
-            d[f"decode_b{B}_ms_per_step_eager"] = round(ms, 3)
-            with Instrument() as ins:
-                ins.extra = {"_keys": B * (decode_ctx + new), "_ctx": B * (decode_ctx + new)}
-                step()
-            eng.graphs = True
-            d[f"decode_b{B}_kernels"] = ins.table(pk)
-            eng.step([], end=ids)
+        d = step_model(m, cfg, pk, g, prompt, decode_ctx, decode_batches, new)
         rec["davasun"] = d
         del eng, m
         torch.cuda.empty_cache()
