@@ -360,10 +360,18 @@ int lia_linear_scan(const void* q, const void* k, int ldqk, const void* v, int l
 int lia_kv_store(const void* k, int ldk, const void* v, int ldv, int act_f32, const int* meta, void* kcache, long long k_slot_stride,
                  void* vcache, long long v_slot_stride, int M, int G, int dim, int vdim, float eps, int norm_values, lia_stream_t stream);
 /* out[row][h] = sum_j softmax_j(cap(q[row][h] . k[j][h / (H/G)] * scale * temp[h])) v[j][h / (H/G)] over 0 <= pos - j < window,
- * cap(s) = softcap * tanh(s / softcap) (softcap <= 0: none) */
+ * cap(s) = softcap * tanh(s / softcap) (softcap <= 0: none).  A block takes rows_per_block consecutive rows and
+ * heads_per_block query heads (<= 8; whole groups of H/G heads, or a divisor of one group), with
+ * rows_per_block * heads_per_block <= 8 * lia_window_attn_pairs_per_warp(vdim) and lia_window_attn_smem_bytes(...) of shared
+ * memory (<= 200 KB).  nsplit > 1 splits every row's keys over nsplit blocks; it needs a workspace of
+ * lia_window_attn_workspace_floats(...) floats and runs a second, combining kernel. */
+int lia_window_attn_pairs_per_warp(int vdim);
+size_t lia_window_attn_smem_bytes(int heads_per_block, int kv_heads_per_block, int rows_per_block, int dim, int vdim);
+size_t lia_window_attn_workspace_floats(int M, int H, int vdim, int nsplit);
 int lia_window_attn(const void* q, int ldq, int act_f32, const void* kcache, long long k_slot_stride, const void* vcache,
-                    long long v_slot_stride, const int* meta, const float* temp, void* out, int M, int H, int G, int dim, int vdim,
-                    int window, float scale, float softcap, lia_stream_t stream);
+                    long long v_slot_stride, const int* meta, const float* temp, void* out, float* workspace, int M, int H, int G, int dim,
+                    int vdim, int window, float scale, float softcap, int heads_per_block, int rows_per_block, int nsplit,
+                    lia_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -121,8 +121,11 @@ _PROTOTYPES = {
                                 c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "lia_kv_store": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int,
                              c_int, c_int, c_float, c_int, c_void_p]),
-    "lia_window_attn": (c_int, [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
-                                c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]),
+    "lia_window_attn_pairs_per_warp": (c_int, [c_int]),
+    "lia_window_attn_smem_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "lia_window_attn_workspace_floats": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "lia_window_attn": (c_int, [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p]),
 }
 
 EXPORTS = tuple(_PROTOTYPES)

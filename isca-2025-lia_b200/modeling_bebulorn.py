@@ -266,9 +266,9 @@ class BebulornForCausalLM:
         return logits
 
     def graph_class(self, max_ctx):
-        """What a decode pass's launches depend on besides the contents of the static buffers: nothing (the attention's
-        window bounds its key range inside the kernel)."""
-        return 0
+        """What a decode pass's launches depend on besides the contents of the static buffers: the number of key ranges each
+        attention layer splits the longest history's window into."""
+        return tuple(sorted({ops.window_attn_split_class(max_ctx, l.mixer.window) for l in self.layers if isinstance(l.mixer, WindowAttentionMixer)}))
 
     def generate(self, input_ids, max_new_tokens=32, chunk=None, **unused):
         """Greedy generation of a batch of prompts through the step engine; returns ids [B, S + new] on the input's device."""

@@ -636,14 +636,50 @@ def kv_store(k, v, meta, kcache, vcache, G, dim, vdim, eps, norm_values=True):
     count_launches()
 
 
-def window_attn(q, kcache, vcache, meta, temp, out, H, G, dim, vdim, window, scale, softcap):
-    """Softmax attention of every row over the last ``window`` cached positions of its sequence (csrc/window_attn.cu)."""
+WINDOW_SPLIT_KEYS, WINDOW_MAX_SPLITS = 64, 32
+
+
+def window_attn_split_class(max_ctx, window):
+    """All that ``window_attn_plan`` takes from the history's length: two lengths of one class launch alike."""
+    return min(min(max_ctx, window) // WINDOW_SPLIT_KEYS, WINDOW_MAX_SPLITS)
+
+
+def window_attn_plan(M, nseg, H, G, dim, vdim, window, max_ctx, sms):
+    """(query heads per block, rows per block, key ranges per row).  Heads: whole groups of H/G query heads while they fit 8
+    warps and 96 KB of staged keys and values, else a divisor of one group.  Rows: a step of prompts lets the rows of a block
+    share the staged keys; a step of single tokens takes one row per block and, when the rows alone do not fill the GPU,
+    splits each row's window over several blocks."""
+    lib = _lib.load()
+    rep = H // G
+    if rep >= 8:
+        hb = max(d for d in range(1, 9) if rep % d == 0)
+    else:
+        ng = min(8 // rep, G)
+        while ng > 1 and lib.lia_window_attn_smem_bytes(ng * rep, ng, max(1, 32 // (ng * rep)), dim, vdim) > 96 * 1024:
+            ng -= 1
+        hb = ng * rep
+    qr = 1 if M < 2 * nseg else max(1, 8 * lib.lia_window_attn_pairs_per_warp(vdim) // hb)
+    blocks = (M + qr - 1) // qr * ((H + hb - 1) // hb)
+    want = (2 * sms + blocks - 1) // blocks
+    nsplit = max(1, min(want, window_attn_split_class(max_ctx, window))) if qr == 1 and max_ctx > 0 else 1
+    return hb, qr, nsplit
+
+
+def window_attn(q, kcache, vcache, meta, temp, out, H, G, dim, vdim, window, scale, softcap, nseg=None, max_ctx=0):
+    """Softmax attention of every row over the last ``window`` cached positions of its sequence (csrc/window_attn.cu).
+    ``nseg``: portions in the step (None: one row each); ``max_ctx``: an upper bound of the rows' history lengths (0: unknown,
+    no split of the keys)."""
     ldq = _rowmajor(q, "q")
     _req(meta, "meta", I32); _req(temp, "temp", F32)
     M = q.shape[0]
     if not (out.is_contiguous() and tuple(out.shape) == (M, H * vdim) and out.dtype == q.dtype == kcache.dtype == vcache.dtype and temp.numel() == H):
         raise _lib.LiaError("window_attn: out must be a contiguous [M, H * vdim] tensor of the activations' dtype, temp [H]")
+    hb, qr, nsplit = window_attn_plan(M, nseg if nseg is not None else M, H, G, dim, vdim, int(window), max_ctx, _sm_count(q.device))
+    ws = None
+    if nsplit > 1:
+        ws = torch.empty(_lib.load().lia_window_attn_workspace_floats(M, H, vdim, nsplit), dtype=F32, device=q.device)
     check(_lib.load().lia_window_attn(_p(q), ldq, _f32(q), _p(kcache), kcache.stride(0), _p(vcache), vcache.stride(0), _p(meta), _p(temp), _p(out),
-                                      M, H, G, dim, vdim, int(window), float(scale), float(softcap), _stream()), "lia_window_attn")
-    count_launches()
+                                      _p(ws), M, H, G, dim, vdim, int(window), float(scale), float(softcap), hb, qr, nsplit, _stream()),
+          "lia_window_attn")
+    count_launches(2 if nsplit > 1 else 1)
     return out

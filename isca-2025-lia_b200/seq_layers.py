@@ -268,7 +268,8 @@ class WindowAttentionMixer:
         q, k, v = (self.proj.part(y, i) for i in range(3))
         ops.kv_store(k, v, batch.meta, kc, vc, self.G, self.dim, self.vdim, self.eps, self.norm_values)
         o = torch.empty(M, self.H * self.vdim, dtype=self.dtype, device=h.device)
-        ops.window_attn(q, kc, vc, batch.meta, self.temp, o, self.H, self.G, self.dim, self.vdim, self.window, self.scale, self.softcap)
+        ops.window_attn(q, kc, vc, batch.meta, self.temp, o, self.H, self.G, self.dim, self.vdim, self.window, self.scale, self.softcap,
+                        nseg=batch.segs.shape[0], max_ctx=batch.max_ctx)
         return self.out(o)
 
 
