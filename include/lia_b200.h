@@ -334,8 +334,12 @@ int lia_moe_plan(const int* idx, int pairs, int E, int n_tiles, int* perm, int* 
 int lia_moe_gemm(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
                  const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N, int K,
                  int up, int act, lia_stream_t stream);
-/* y[m] = sum_t ypair[m * top + t] (+ shared[m], may be NULL), fp32 */
-int lia_moe_combine(const float* ypair, const void* shared, int shared_f32, float* y, int M, int W, int top, lia_stream_t stream);
+/* dst[place] = src[perm[place] / top] (zeros where perm is -1): the experts' inputs in the plan's order */
+int lia_moe_gather(const void* src, int act_f32, const int* perm, void* dst, int places, int W, int top, lia_stream_t stream);
+/* y[m] = sum_t f(m * top + t) (+ shared[m], may be NULL), fp32; f(pair) = ypair[pair], or, when pos_of is given,
+ * wt[pair] * ypair[pos_of[pair]] */
+int lia_moe_combine(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int shared_f32, float* y, int M,
+                    int W, int top, lia_stream_t stream);
 
 /* Short causal convolution (taps <= 8, weights [channels][taps], last column = current token) + SiLU over the q | k | v
  * channels of a projection's output y (row stride ld, column offsets given; q and k have G heads of dim, v has H of vdim);

@@ -79,7 +79,7 @@ class Instrument:
     NAMES = ("gemm", "linear_plain", "linear_small", "mlstm_scan", "headnorm_gate", "latent_prep", "latent_attn", "clamped_glu",
              "rms_add_norm", "embed_rmsnorm", "rms_gather", "layernorm", "attn_prefill", "attn_decode", "embed", "argmax", "argmax_f32",
              "linear_scan", "conv_prep", "conv_state_update", "kv_store", "window_attn", "ln_add_norm", "embed_rows", "ln_gather", "gated_act",
-             "router_topk", "moe_plan", "moe_gemm", "moe_combine")
+             "router_topk", "moe_plan", "moe_gemm", "moe_gather", "moe_combine")
 
     def __init__(self):
         self.records, self.saved, self.extra = [], {}, {}

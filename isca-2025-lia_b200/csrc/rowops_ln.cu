@@ -8,6 +8,7 @@
 //   moe_plan       (token, choice) pairs grouped by expert into row tiles
 //   moe_gemm       one projection of every expert over its own rows (gather on the way in, activation or routing weight on
 //                  the way out); moe_fewrows does the same for a handful of pairs with one warp per output
+//   moe_gather     the experts' input rows laid out in the plan's order, for projections that want contiguous rows
 //   moe_combine    y[token] = sum over its choices (+ the shared expert's output)
 // LN is (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b with fp32 statistics taken in two passes over a staged row.
 #include <math.h>
@@ -323,15 +324,33 @@ __global__ void __launch_bounds__(128) moe_fewrows_kernel(const TA* __restrict__
   if (lane == 0) stf(C + (size_t)p * ldc + n, UP ? act_apply(acc, act) : acc * wt[p]);
 }
 
-// y[m][c] = sum_t ypair[m * top + t][c] (in the order of t) + shared[m][c]
-template <typename TS>
-__global__ void moe_combine_kernel(const float* __restrict__ ypair, const TS* __restrict__ shared, float* __restrict__ y, int M, int W, int top) {
+// dst[place] = src[perm[place] / top] for every place of the plan, zeros in the padding: the experts' inputs, expert by expert
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ src, const int* __restrict__ perm, T* __restrict__ dst, int places, int W, int top) {
+  const size_t n = (size_t)places * W;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / W;
+    const int c = (int)(e - r * W);
+    const int p = perm[r];
+    dst[e] = p < 0 ? T(0.f) : src[(size_t)(p / top) * W + c];
+  }
+}
+
+// y[m][c] = sum_t f(m * top + t)[c] (in the order of t) + shared[m][c];  f(pair) = ypair[pair], or, with a plan,
+// wt[pair] * ypair[pos_of[pair]] (the experts' outputs still in the plan's order and not yet weighted)
+template <typename TY, typename TS>
+__global__ void moe_combine_kernel(const TY* __restrict__ ypair, const int* __restrict__ pos_of, const float* __restrict__ wt,
+                                   const TS* __restrict__ shared, float* __restrict__ y, int M, int W, int top) {
   const size_t n = (size_t)M * W;
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
     const size_t m = e / W;
     const int c = (int)(e - m * W);
     float s = 0.f;
-    for (int t = 0; t < top; ++t) s += ypair[(m * top + t) * W + c];
+    for (int t = 0; t < top; ++t) {
+      const size_t pair = m * top + t;
+      if (pos_of) s = fmaf(wt[pair], ldf(ypair + (size_t)pos_of[pair] * W + c), s);
+      else s += ldf(ypair + pair * W + c);
+    }
     if (shared) s += ldf(shared + e);
     y[e] = s;
   }
@@ -460,12 +479,27 @@ extern "C" int lia_moe_gemm(const void* A, int a_f32, int lda, const void* W, in
   return LIA_OK;
 }
 
-extern "C" int lia_moe_combine(const float* ypair, const void* shared, int shared_f32, float* y, int M, int W, int top, lia_stream_t stream_) {
+extern "C" int lia_moe_gather(const void* src, int act_f32, const int* perm, void* dst, int places, int W, int top, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  LIA_CHECK_ARG(ypair && y && M > 0 && W > 0 && top > 0, "lia_moe_combine: bad arguments");
+  LIA_CHECK_ARG(src && perm && dst && places > 0 && W > 0 && top > 0, "lia_moe_gather: bad arguments");
+  const unsigned blocks = capped_blocks((size_t)places * W);
+  if (act_f32) moe_gather_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(src), perm, reinterpret_cast<float*>(dst), places, W, top);
+  else moe_gather_kernel<bf16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(src), perm, reinterpret_cast<bf16*>(dst), places, W, top);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_moe_combine(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int shared_f32, float* y,
+                               int M, int W, int top, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(ypair && y && M > 0 && W > 0 && top > 0 && (!pos_of || wt), "lia_moe_combine: bad arguments");
   const unsigned blocks = capped_blocks((size_t)M * W);
-  if (shared_f32) moe_combine_kernel<float><<<blocks, 256, 0, stream>>>(ypair, reinterpret_cast<const float*>(shared), y, M, W, top);
-  else moe_combine_kernel<bf16><<<blocks, 256, 0, stream>>>(ypair, reinterpret_cast<const bf16*>(shared), y, M, W, top);
+#define LIA_MC(TY, TS) moe_combine_kernel<TY, TS><<<blocks, 256, 0, stream>>>(reinterpret_cast<const TY*>(ypair), pos_of, wt, reinterpret_cast<const TS*>(shared), y, M, W, top)
+  if (ypair_f32 && shared_f32) LIA_MC(float, float);
+  else if (ypair_f32) LIA_MC(float, bf16);
+  else if (shared_f32) LIA_MC(bf16, float);
+  else LIA_MC(bf16, bf16);
+#undef LIA_MC
   LIA_LAUNCH_CHECK();
   return LIA_OK;
 }

@@ -566,13 +566,27 @@ def moe_gemm(a, w, out, idx, wt, top, up, act=ACT_NONE, perm=None, tile_expert=N
     return out
 
 
-def moe_combine(ypair, shared, y, top):
-    _req(ypair, "ypair", F32); _req(y, "y", F32)
+def moe_gather(src, perm, dst, top):
+    """dst[place] = src[perm[place] // top], zeros in the plan's padding."""
+    _req(perm, "perm", I32)
+    if not (src.is_contiguous() and dst.is_contiguous() and src.dtype == dst.dtype and dst.shape[0] == perm.numel() and dst.shape[1] == src.shape[1]):
+        raise _lib.LiaError("moe_gather: dst must be a contiguous [places, W] tensor of the source's dtype")
+    check(_lib.load().lia_moe_gather(_p(src), _f32(src), _p(perm), _p(dst), perm.numel(), src.shape[1], top, _stream()), "lia_moe_gather")
+    count_launches()
+    return dst
+
+
+def moe_combine(ypair, shared, y, top, pos_of=None, wt=None):
+    """y[m] = sum over the token's choices (+ the shared expert's output).  Without a plan ``ypair`` holds the weighted
+    outputs pair by pair; with ``pos_of`` and ``wt`` it holds the unweighted outputs in the plan's order."""
+    _dev(ypair, "ypair"); _req(y, "y", F32)
     M, W = y.shape
     if shared is not None and not (shared.is_contiguous() and tuple(shared.shape) == (M, W)):
         raise _lib.LiaError("moe_combine: the shared expert's output must be a contiguous [M, W] tensor")
-    check(_lib.load().lia_moe_combine(_p(ypair), _p(shared), _f32(shared) if shared is not None else 1, _p(y), M, W, top, _stream()),
-          "lia_moe_combine")
+    if not ypair.is_contiguous() or ypair.shape[1] != W or (pos_of is None) != (wt is None):
+        raise _lib.LiaError("moe_combine: ypair must be a contiguous [.., W] tensor; pos_of and wt go together")
+    check(_lib.load().lia_moe_combine(_p(ypair), _f32(ypair), _p(pos_of), _p(wt), _p(shared), _f32(shared) if shared is not None else 1, _p(y), M, W,
+                                      top, _stream()), "lia_moe_combine")
     count_launches()
     return y
 

@@ -310,7 +310,8 @@ class MoEFeedForward:
     (no host round trip) and each projection runs as one grouped launch; a handful of pairs (decoding) take the form with one
     warp per output instead.  The result is fp32."""
 
-    FEW_PAIRS = 48
+    FEW_PAIRS = 48            # up to here: one warp per output, no plan
+    TENSOR_CORE_PAIRS = 512   # from here (bf16, sizes that are multiples of 8): every expert's rows through the tensor-core GEMM
 
     def __init__(self, router_w, experts_w, top, ff, act, shared, dtype, device):
         self.E, self.top, self.ff, self.act, self.dtype = len(experts_w), int(top), ff, act, dtype
@@ -320,6 +321,49 @@ class MoEFeedForward:
         self.w_up = torch.stack([e["up"] for e in experts_w]).to(device=device, dtype=dtype).contiguous()         # [E, ff, W]
         self.w_down = torch.stack([e["down"] for e in experts_w]).to(device=device, dtype=dtype).contiguous()     # [E, W, ff]
         self.shared = shared
+        W = self.w_up.shape[2]
+        self.tensor_core = dtype == BF16 and W % 8 == 0 and ff % 8 == 0 and os.environ.get("LIA_PLAIN_LINEAR", "0") == "0"
+
+    def _workspace(self, M, N, K, device):
+        key = (device, M <= 128)
+        need = ops.GemmWorkspace.bytes_for([(M, N, K)])
+        ws = Linear._gemm_ws.get(key)
+        if ws is None or ws.buf.numel() < need:
+            ws = Linear._gemm_ws[key] = ops.GemmWorkspace(need, device)
+        return ws
+
+    def _experts_tensor_core(self, h, idx, wt, y):
+        """Prompts: the pairs grouped by expert (tiles of 64 rows), the rows gathered into that order, then one tensor-core
+        GEMM per expert and projection on its contiguous rows.  The tile table comes to the host once per call (the only
+        round trip; decode steps never take this path, so they stay capturable)."""
+        M, W = h.shape
+        E, top, ff, dev = self.E, self.top, self.ff, h.device
+        pairs = M * top
+        n_tiles, tm = ops.moe_tiles(pairs, E)
+        perm = torch.empty(n_tiles * tm, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(n_tiles, dtype=torch.int32, device=dev)
+        pos_of = torch.empty(pairs, dtype=torch.int32, device=dev)
+        ops.moe_plan(idx, E, perm, tile_expert, pos_of)
+        xs = torch.empty(n_tiles * tm, W, dtype=self.dtype, device=dev)
+        ops.moe_gather(h, perm, xs, top)
+        counts = torch.bincount(tile_expert.cpu().long() + 1, minlength=E + 1)[1:].tolist()          # tiles per expert
+        used = sum(counts) * tm
+        up = torch.empty(used, ff, dtype=self.dtype, device=dev)
+        at = 0
+        for e, n in enumerate(counts):
+            if n:
+                ops.gemm(xs[at:at + n * tm], self.w_up[e], None, out=up[at:at + n * tm], workspace=self._workspace(n * tm, ff, W, dev))
+                at += n * tm
+        mid = torch.empty(used, ff, dtype=self.dtype, device=dev)
+        ops.gated_act(up, ff, mid, self.act)
+        ys = torch.empty(used, W, dtype=self.dtype, device=dev)
+        at = 0
+        for e, n in enumerate(counts):
+            if n:
+                ops.gemm(mid[at:at + n * tm], self.w_down[e], None, out=ys[at:at + n * tm], workspace=self._workspace(n * tm, W, ff, dev))
+                at += n * tm
+        ops.moe_combine(ys, self.shared(h) if self.shared is not None else None, y, top, pos_of=pos_of, wt=wt)
+        return y
 
     def __call__(self, h):
         M, W, dev = h.shape[0], h.shape[1], h.device
@@ -330,6 +374,9 @@ class MoEFeedForward:
         wt = torch.empty(M, top, dtype=F32, device=dev)
         ops.router_topk(logits, top, idx, wt)
         pairs = M * top
+        y = torch.empty(M, W, dtype=F32, device=dev)
+        if self.tensor_core and pairs >= self.TENSOR_CORE_PAIRS and h.is_contiguous() and not torch.cuda.is_current_stream_capturing():
+            return self._experts_tensor_core(h, idx, wt, y)
         ypair = torch.empty(pairs, W, dtype=F32, device=dev)
         if pairs <= self.FEW_PAIRS:
             mid = torch.empty(pairs, self.ff, dtype=self.dtype, device=dev)
@@ -344,6 +391,5 @@ class MoEFeedForward:
             mid = torch.empty(n_tiles * tm, self.ff, dtype=self.dtype, device=dev)
             ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, perm, tile_expert)
             ops.moe_gemm(mid, self.w_down, ypair, idx, wt, top, False, ops.ACT_NONE, perm, tile_expert)
-        y = torch.empty(M, W, dtype=F32, device=dev)
         ops.moe_combine(ypair, self.shared(h) if self.shared is not None else None, y, top)
         return y

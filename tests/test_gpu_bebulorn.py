@@ -135,13 +135,17 @@ def test_router_picks_and_weights(M, E, top):
 
 
 @pytest.mark.parametrize("M,E,top,shared,dtype", [(5, 6, 2, 12, F32), (100, 6, 2, 12, F32), (130, 3, 3, None, F32), (64, 9, 1, 5, F32),
-                                                  (200, 4, 2, 16, BF16), (3, 4, 2, 16, BF16)])
+                                                  (200, 4, 2, 16, BF16), (3, 4, 2, 16, BF16), (700, 5, 2, 16, BF16), (300, 7, 1, None, BF16)])
 def test_mixture_of_experts_in_both_forms(M, E, top, shared, dtype):
-    """Few (token, choice) pairs take one warp per output, many are grouped by expert into tiles; both against the oracle's
+    """Few (token, choice) pairs take one warp per output, many are grouped by expert into tiles (in bf16 from 512 pairs on:
+    gathered expert by expert and run through the tensor-core GEMM, one expert left without a token); all against the oracle's
     token-by-token loop.  The router's weights are scaled up so that the choice is never a near-tie."""
     g = gen(3)
     W, ff = 40, 24
     w = {"router": bf(torch.randn(E, W, generator=g) * 2.0)}
+    if M >= 300:
+        w["router"][E - 1] = 0.0
+        w["router"][E - 1, 0] = -50.0            # with h[:, 0] = 1 below, the last expert is never chosen
     for e in range(E):
         w[f"e{e}.up"], w[f"e{e}.down"] = bf(torch.randn(ff, W, generator=g) * W ** -0.5), bf(torch.randn(W, ff, generator=g) * ff ** -0.5)
     cfg = {"router": {"experts": E, "top": top}, "expert": {"ff": ff}}
@@ -152,6 +156,8 @@ def test_mixture_of_experts_in_both_forms(M, E, top, shared, dtype):
         sh = PlainMLP({"up": w["shared.up"], "down": w["shared.down"]}, shared, ops.ACT_GELU_ERF, dtype, DEV)
     m = MoEFeedForward(w["router"], [{"up": w[f"e{e}.up"], "down": w[f"e{e}.down"]} for e in range(E)], top, ff, ops.ACT_GELU_ERF, sh, dtype, DEV)
     h = bf(torch.randn(M, W, generator=g))
+    if M >= 300:
+        h[:, 0] = 1.0
     got = m(h.to(device=DEV, dtype=dtype))
     assert got.dtype == F32
     want = O.moe(h.double(), {k: v.double() for k, v in w.items()}, "", cfg)
