@@ -60,8 +60,11 @@ class BebulornConfig:
             m = l["mixer"]
             if l["type"] != "lightning" and m["heads"] % m["kv_heads"]:
                 raise ValueError(f"layer {i}: {m['heads']} heads do not divide into {m['kv_heads']} groups")
-            if l["type"] == "lightning" and len(m["decay"]) != m["heads"]:
-                raise ValueError(f"layer {i}: {len(m['decay'])} decays for {m['heads']} heads")
+            if l["type"] == "lightning":
+                if not isinstance(m["decay"], (list, tuple)):
+                    m["decay"] = [float(m["decay"])] * m["heads"]          # one decay for all heads
+                if len(m["decay"]) != m["heads"]:
+                    raise ValueError(f"layer {i}: {len(m['decay'])} decays for {m['heads']} heads")
         loop = c.get("loop") or {"start": 0, "stop": 0, "times": 1}
         start, stop, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
         if not (0 <= start <= stop <= len(layers)) or times < 1:
@@ -165,7 +168,7 @@ class BebulornForCausalLM:
             if l["type"] == "lightning":
                 mixer = DecayLinearAttentionMixer(w, m["heads"], m["dim"], m["vdim"], m["decay"], cfg.norm_eps, dt, dev)
             elif l["type"] == "attention":
-                mixer = WindowAttentionMixer(w, m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"], m["scale"], m["softcap"],
+                mixer = WindowAttentionMixer(w, m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"], m["scale"], m.get("softcap", 0.0),
                                              cfg.norm_eps, dt, dev)
             else:
                 mixer = DeltaRuleMixer(w, m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], cfg.norm_eps, dt, dev)
