@@ -124,6 +124,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
                        k_slot_stride % VEC == 0 && v_slot_stride % VEC == 0;
   const bool vec_k = aligned && a.dim % VEC == 0 && a.dim % 4 == 0, vec_v = aligned && a.vdim % VEC == 0;
   const bool dot4 = a.dim % 4 == 0;
+  const bool same_head = NWARP % nh == 0 && PP > 1;           // pair p = warp + 8 s belongs to head p % nh = warp % nh for every s
 
   int r = r_begin;
   while (r < r_end) {
@@ -156,6 +157,82 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
       stage_rows(kc, a.G, a.dim, g_lo, ng, j0, nk, ks, DKS, vec_k);
       stage_rows(vc, a.G, a.vdim, g_lo, ng, j0, nk, vs, a.vdim, vec_v);
       __syncthreads();
+      if (same_head) {
+        // All pairs of this warp are rows of ONE query head (nh divides the warp count): a staged key or value row is read
+        // from shared memory once and serves the PP rows.
+        const int hh = warp % nh, h = h0 + hh, gi = h / rep - g_lo;
+        const float sc_mul = a.scale * temp[h];
+        bool active[PP];
+        int lo_min = 0x7fffffff, pos_max = -1;
+#pragma unroll
+        for (int s = 0; s < PP; ++s) {
+          const int p = warp + NWARP * s;
+          const int pos = pos_first + p / nh, lo = max(0, pos - a.window + 1);
+          active[s] = p < npairs && j0 <= pos && j0 + nk - 1 >= lo;
+          if (active[s]) {
+            lo_min = min(lo_min, lo);
+            pos_max = max(pos_max, pos);
+          }
+        }
+        if (pos_max >= 0) {
+          float dot[PP];
+#pragma unroll
+          for (int s = 0; s < PP; ++s) dot[s] = 0.f;
+          const float* kr = ks + (gi * TK + lane) * DKS;
+          if (dot4) {
+            const float4* k4 = reinterpret_cast<const float4*>(kr);
+            for (int d = 0; d < a.dim / 4; ++d) {
+              const float4 y = k4[d];
+#pragma unroll
+              for (int s = 0; s < PP; ++s) {
+                const float4 x = reinterpret_cast<const float4*>(qs + (warp + NWARP * s) * a.dim)[d];
+                dot[s] = fmaf(x.x, y.x, fmaf(x.y, y.y, fmaf(x.z, y.z, fmaf(x.w, y.w, dot[s]))));
+              }
+            }
+          } else {
+            for (int d = 0; d < a.dim; ++d) {
+              const float y = kr[d];
+#pragma unroll
+              for (int s = 0; s < PP; ++s) dot[s] = fmaf(qs[(warp + NWARP * s) * a.dim + d], y, dot[s]);
+            }
+          }
+          float pr[PP];
+#pragma unroll
+          for (int s = 0; s < PP; ++s) {
+            pr[s] = 0.f;
+            if (!active[s]) continue;                         // warp-uniform
+            const int pos = pos_first + (warp + NWARP * s) / nh, lo = max(0, pos - a.window + 1);
+            float sc = dot[s] * sc_mul;
+            if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+            const int j = j0 + lane;
+            if (lane >= nk || j < lo || j > pos) sc = -INFINITY;
+            const float m_new = fmaxf(m_run[s], warp_max(sc));  // finite: at least one key of the stage is visible
+            pr[s] = expf(sc - m_new);
+            const float al = expf(m_run[s] - m_new);
+            l_run[s] = l_run[s] * al + warp_sum(pr[s]);
+            m_run[s] = m_new;
+#pragma unroll
+            for (int c = 0; c < VR; ++c) acc[s][c] *= al;
+          }
+          const float* vr = vs + gi * TK * a.vdim;
+          const int jj_end = min(nk - 1, pos_max - j0);
+          for (int jj = max(0, lo_min - j0); jj <= jj_end; ++jj) {
+            float vv[VR];
+#pragma unroll
+            for (int c = 0; c < VR; ++c) {
+              const int ch = lane + 32 * c;
+              vv[c] = ch < a.vdim ? vr[jj * a.vdim + ch] : 0.f;
+            }
+#pragma unroll
+            for (int s = 0; s < PP; ++s) {
+              const float pw = __shfl_sync(0xffffffffu, pr[s], jj);   // 0 for a row that does not see key jj
+#pragma unroll
+              for (int c = 0; c < VR; ++c) acc[s][c] = fmaf(pw, vv[c], acc[s][c]);
+            }
+          }
+        }
+        continue;
+      }
 #pragma unroll
       for (int s = 0; s < PP; ++s) {
         const int p = warp + NWARP * s;
