@@ -8,7 +8,8 @@
 // is contiguous.  A warp keeps CW columns in registers for the whole portion, lane l owning rows l, l + 32, ...; a token
 // costs one butterfly reduction (CW sums for DECAY; 2 CW + 1 for DELTA, where S'^T k, S'^T q and k . q are reduced together
 // and o_t = g S_{t-1}^T q + u (k . q) needs no second pass).  The 8 warps of a block share the q and k of their head through
-// a double-buffered shared-memory stage of TB tokens fetched while the previous TB are processed.  q and k may belong to a
+// a double-buffered shared-memory stage of TB tokens fetched while the previous TB are processed (128-bit loads where the rows
+// allow them).  q and k may belong to a
 // smaller number of heads than v (head h reads q/k head h / (H / G)); an activation (SiLU) can be applied as the inputs are
 // staged, so that a projection's output feeds the recurrence directly.
 //
@@ -127,19 +128,46 @@ template <> struct Raw<bf16> {
   static __device__ __forceinline__ float to_float(unsigned short u) { return __uint_as_float((unsigned)u << 16); }
 };
 
+// 128-bit stage load (raw bits, same reasoning) and its unpacking into VEC floats
+__device__ __forceinline__ uint4 ld_raw128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+template <typename T> struct Vec128;
+template <> struct Vec128<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(uint4 v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+  }
+};
+template <> struct Vec128<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(uint4 v, float* f) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+  }
+};
+
 constexpr int TB = 8;            // tokens per stage
 constexpr int CW = 2;            // columns of S per warp
 constexpr int NW = 8;            // warps per block
 constexpr int CB = CW * NW;      // columns per block
 
-template <typename T, int DR, bool DELTA>
+// VL: the stage is fetched with 128-bit loads (the host checked that every q / k / v segment of VEC numbers starts on a
+// 16-byte boundary and lies wholly inside or outside its row).
+template <typename T, int DR, bool DELTA, bool VL>
 __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, int ldqk, const T* __restrict__ v, int ldv,
                                                               int in_silu, const float* __restrict__ decay, const float* __restrict__ gates,
                                                               float* __restrict__ St, const int* __restrict__ segs, int H, int G, int dim, int vdim,
                                                               float* __restrict__ o) {
   constexpr int DP = DR * 32;                    // dim padded to whole warps
   constexpr int ROWF = 2 * DP + CB + 4;          // floats of one staged token: q | k | v (this block's columns) | beta | g | 2 pad
-  constexpr int NST = (TB * ROWF + NW * 32 - 1) / (NW * 32);
+  constexpr int VEC = Vec128<T>::N;
+  constexpr int CH = (2 * DP + CB) / VEC;        // 128-bit segments of one staged token
+  constexpr int NST = VL ? (TB * CH + NW * 32 - 1) / (NW * 32) : (TB * ROWF + NW * 32 - 1) / (NW * 32);
   extern __shared__ __align__(16) float stage[]; // [2][TB][ROWF]
   const int seg = blockIdx.z, h = blockIdx.y, colb = blockIdx.x * CB;
   const int hk = h / (H / G);
@@ -157,9 +185,29 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
   }
   const float dec = DELTA ? 0.f : decay[h];
 
-  typename Raw<T>::type buf[NST];
+  typename Raw<T>::type buf[VL ? 1 : NST];
+  uint4 vbuf[VL ? NST : 1];
   float gbuf = 0.f;
   auto fetch = [&](int g) {
+    if constexpr (VL) {
+#pragma unroll
+      for (int s = 0; s < NST; ++s) {
+        const int e = threadIdx.x + s * NW * 32;
+        const T* p = nullptr;
+        if (e < TB * CH) {
+          const int t = e / CH, j = (e - t * CH) * VEC;
+          const int tok = g * TB + t;
+          if (tok < len) {
+            const size_t row = (size_t)(row0 + tok);
+            if (j < DP) { if (j < dim) p = q + row * ldqk + hk * dim + j; }
+            else if (j < 2 * DP) { if (j - DP < dim) p = k + row * ldqk + hk * dim + (j - DP); }
+            else if (colb + j - 2 * DP < vdim) p = v + row * ldv + h * vdim + colb + (j - 2 * DP);
+          }
+        }
+        vbuf[s] = make_uint4(0u, 0u, 0u, 0u);
+        if (p != nullptr) vbuf[s] = ld_raw128(p);
+      }
+    } else {
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
       const int e = threadIdx.x + s * NW * 32;
@@ -177,6 +225,7 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
       buf[s] = typename Raw<T>::type(0);
       if (p != nullptr) buf[s] = Raw<T>::ld(p);
     }
+    }
     if (DELTA && threadIdx.x < 2 * TB) {
       const int tok = g * TB + (threadIdx.x >> 1);
       gbuf = 0.f;
@@ -184,6 +233,24 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
     }
   };
   auto put = [&](int b) {
+    if constexpr (VL) {
+#pragma unroll
+      for (int s = 0; s < NST; ++s) {
+        const int e = threadIdx.x + s * NW * 32;
+        if (e < TB * CH) {
+          const int t = e / CH, j = (e - t * CH) * VEC;
+          float f[VEC];
+          Vec128<T>::unpack(vbuf[s], f);
+          if (in_silu) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) f[i] = silu(f[i]);
+          }
+          float* dst = stage + b * TB * ROWF + t * ROWF + j;
+#pragma unroll
+          for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+        }
+      }
+    } else {
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
       const int e = threadIdx.x + s * NW * 32;
@@ -194,6 +261,7 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
           stage[b * TB * ROWF + e] = in_silu ? silu(x) : x;
         }
       }
+    }
     }
     if (DELTA && threadIdx.x < 2 * TB) stage[b * TB * ROWF + (threadIdx.x >> 1) * ROWF + 2 * DP + CB + (threadIdx.x & 1)] = gbuf;
   };
@@ -276,22 +344,32 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
   }
 }
 
-template <typename T, int DR>
-int launch_scan(const void* q, const void* k, int ldqk, const void* v, int ldv, int in_silu, const float* decay, const float* gates, float* St,
-                const int* segs, int nseg, int H, int G, int dim, int vdim, float* o, cudaStream_t stream) {
+template <typename T, int DR, bool VL>
+int launch_scan_as(const void* q, const void* k, int ldqk, const void* v, int ldv, int in_silu, const float* decay, const float* gates, float* St,
+                   const int* segs, int nseg, int H, int G, int dim, int vdim, float* o, cudaStream_t stream) {
   const size_t smem = (size_t)2 * TB * (2 * DR * 32 + CB + 4) * sizeof(float);
   dim3 grid((vdim + CB - 1) / CB, H, nseg);
   if (gates != nullptr) {
-    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(linear_scan_kernel<T, DR, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    linear_scan_kernel<T, DR, true><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), ldqk,
-                                                                    reinterpret_cast<const T*>(v), ldv, in_silu, decay, gates, St, segs, H, G, dim, vdim, o);
+    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(linear_scan_kernel<T, DR, true, VL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    linear_scan_kernel<T, DR, true, VL><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), ldqk,
+                                                                        reinterpret_cast<const T*>(v), ldv, in_silu, decay, gates, St, segs, H, G, dim, vdim, o);
   } else {
-    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(linear_scan_kernel<T, DR, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    linear_scan_kernel<T, DR, false><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), ldqk,
-                                                                     reinterpret_cast<const T*>(v), ldv, in_silu, decay, gates, St, segs, H, G, dim, vdim, o);
+    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(linear_scan_kernel<T, DR, false, VL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    linear_scan_kernel<T, DR, false, VL><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), ldqk,
+                                                                         reinterpret_cast<const T*>(v), ldv, in_silu, decay, gates, St, segs, H, G, dim, vdim, o);
   }
   LIA_LAUNCH_CHECK();
   return LIA_OK;
+}
+
+template <typename T, int DR>
+int launch_scan(const void* q, const void* k, int ldqk, const void* v, int ldv, int in_silu, const float* decay, const float* gates, float* St,
+                const int* segs, int nseg, int H, int G, int dim, int vdim, float* o, cudaStream_t stream) {
+  constexpr int VEC = Vec128<T>::N;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) % 16 == 0) &&
+                       ldqk % VEC == 0 && ldv % VEC == 0 && dim % VEC == 0 && vdim % VEC == 0;
+  if (aligned) return launch_scan_as<T, DR, true>(q, k, ldqk, v, ldv, in_silu, decay, gates, St, segs, nseg, H, G, dim, vdim, o, stream);
+  return launch_scan_as<T, DR, false>(q, k, ldqk, v, ldv, in_silu, decay, gates, St, segs, nseg, H, G, dim, vdim, o, stream);
 }
 
 template <typename T>

@@ -174,8 +174,7 @@ class ClampedGLU:
 
 class DecayLinearAttentionMixer:
     """Linear attention with a fixed decay per head ("lightning" attention): q, k, v = act(Wq h), act(Wk h), act(Wv h);
-    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (csrc/linear_scan.cu, which applies ``act`` = SiLU as it reads the
-    projection); the concatenated heads RMS-normed together with a per-channel weight, times sigmoid(Wg h), then Wo."""
+    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (csrc/linear_scan.cu), act = SiLU; the concatenated heads RMS-normed together with a per-channel weight, times sigmoid(Wg h), then Wo."""
 
     def __init__(self, w, heads, dim, vdim, decay, norm_eps, dtype, device):
         if len(decay) != heads:
@@ -193,9 +192,14 @@ class DecayLinearAttentionMixer:
         (S,) = state
         M, H = h.shape[0], self.H
         y = self.proj(h)
-        q, k, v, g = (self.proj.part(y, i) for i in range(4))
+        g = self.proj.part(y, 3)
+        # SiLU of q | k | v in one pass over their columns (every block of the scan that shares a head would repeat it otherwise)
+        F_, offs = self.proj.offsets[3], self.proj.offsets
+        act = torch.empty(M, F_, dtype=self.dtype, device=h.device)
+        ops.gated_act(y, F_, act, ops.ACT_SILU)
+        q, k, v = act[:, offs[0]:offs[0] + H * self.dim], act[:, offs[1]:offs[1] + H * self.dim], act[:, offs[2]:offs[2] + H * self.vdim]
         o = torch.empty(M, H * self.vdim, dtype=F32, device=h.device)
-        ops.linear_scan(q, k, v, S, batch.segs, H, H, self.dim, self.vdim, o, decay=self.decay, in_silu=True)
+        ops.linear_scan(q, k, v, S, batch.segs, H, H, self.dim, self.vdim, o, decay=self.decay)
         on = torch.empty(M, H * self.vdim, dtype=self.dtype, device=h.device)
         ops.headnorm_gate(o, self.norm_w, g, on, 1, H * self.vdim, self.eps)       # one norm over all heads
         return self.out(on)

@@ -230,7 +230,7 @@ def _attention_reference(q, kc, vc, pos, H, G, window, scale, temp, cap):
 
 
 @pytest.mark.parametrize("H,G,dim,vdim,window,dtype", [(1, 1, 12, 10, 5, F32), (6, 2, 24, 16, 33, F32), (9, 3, 72, 80, 1, F32),
-                                                       (4, 4, 8, 136, 64, F32), (16, 2, 16, 40, 32, F32), (6, 6, 48, 48, 31, BF16)])
+                                                       (4, 4, 8, 136, 64, F32), (16, 2, 16, 40, 32, F32), (5, 5, 40, 56, 31, BF16)])
 def test_window_attention_kernel_at_the_edges(H, G, dim, vdim, window, dtype):
     g = gen(6)
     cap_rows = 200
