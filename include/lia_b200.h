@@ -336,6 +336,10 @@ int lia_moe_gemm(const void* A, int a_f32, int lda, const void* W, int w_f32, lo
                  int up, int act, lia_stream_t stream);
 /* dst[place] = src[perm[place] / top] (zeros where perm is -1): the experts' inputs in the plan's order */
 int lia_moe_gather(const void* src, int act_f32, const int* perm, void* dst, int places, int W, int top, lia_stream_t stream);
+/* C[rows of expert e] = A[rows of expert e] @ W[e].T (bf16, lia_gemm_bf16 per expert): expert e owns the next
+ * tiles_per_expert[e] * tile_rows rows (tiles_per_expert is a HOST array); workspace as for lia_gemm_bf16 at the largest M. */
+int lia_moe_expert_gemms(const void* A, const void* W, long long w_expert_stride, void* C, const int* tiles_per_expert, int E, int tile_rows,
+                         int N, int K, void* workspace, size_t workspace_bytes, lia_stream_t stream);
 /* y[m] = sum_t f(m * top + t) (+ shared[m], may be NULL), fp32; f(pair) = ypair[pair], or, when pos_of is given,
  * wt[pair] * ypair[pos_of[pair]] */
 int lia_moe_combine(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int shared_f32, float* y, int M,

@@ -113,6 +113,8 @@ _PROTOTYPES = {
     "lia_moe_gemm": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "lia_moe_gather": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "lia_moe_expert_gemms": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, POINTER(c_int), c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                                     c_void_p]),
     "lia_moe_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "lia_conv_prep": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]),

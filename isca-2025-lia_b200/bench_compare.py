@@ -63,6 +63,10 @@ def _cost(name, a, kw):
         touched = min(w.shape[0], pairs)
         kind = "tc" if x.dtype == BF16 and pairs > 64 else "mem"
         return 2.0 * pairs * N * K, pairs * (K * x.element_size() + N * out.element_size()) + touched * N * K * w.element_size(), kind
+    if name == "moe_expert_gemms":
+        x, w, counts, tm = a[0], a[1], a[3], a[4]
+        rows, N, K = sum(counts) * tm, w.shape[1], w.shape[2]
+        return 2.0 * rows * N * K, 2.0 * (rows * K + sum(1 for n in counts if n) * N * K + rows * N), "tc"
     if name == "attn_prefill":
         q, kc, B, S = a[0], a[1], a[3], a[4]
         H, d = kc.shape[2], kc.shape[3]
@@ -79,7 +83,7 @@ class Instrument:
     NAMES = ("gemm", "linear_plain", "linear_small", "mlstm_scan", "headnorm_gate", "latent_prep", "latent_attn", "clamped_glu",
              "rms_add_norm", "embed_rmsnorm", "rms_gather", "layernorm", "attn_prefill", "attn_decode", "embed", "argmax", "argmax_f32",
              "linear_scan", "conv_prep", "conv_state_update", "kv_store", "window_attn", "ln_add_norm", "embed_rows", "ln_gather", "gated_act",
-             "router_topk", "moe_plan", "moe_gemm", "moe_gather", "moe_combine")
+             "router_topk", "moe_plan", "moe_gemm", "moe_gather", "moe_expert_gemms", "moe_combine")
 
     def __init__(self):
         self.records, self.saved, self.extra = [], {}, {}

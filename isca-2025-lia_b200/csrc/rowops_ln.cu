@@ -489,6 +489,26 @@ extern "C" int lia_moe_gather(const void* src, int act_f32, const int* perm, voi
   return LIA_OK;
 }
 
+// The tensor-core form: every expert's contiguous rows of the gathered input through lia_gemm_bf16, one launch per expert that has
+// rows, issued from here so that the launches follow each other without a trip through the caller's interpreter.
+extern "C" int lia_moe_expert_gemms(const void* A, const void* W, long long w_expert_stride, void* C, const int* tiles_per_expert, int E,
+                                    int tile_rows, int N, int K, void* workspace, size_t workspace_bytes, lia_stream_t stream_) {
+  LIA_CHECK_ARG(A && W && C && tiles_per_expert && E > 0 && tile_rows > 0 && N > 0 && K > 0, "lia_moe_expert_gemms: bad arguments");
+  const bf16* a = reinterpret_cast<const bf16*>(A);
+  const bf16* w = reinterpret_cast<const bf16*>(W);
+  bf16* c = reinterpret_cast<bf16*>(C);
+  size_t at = 0;
+  for (int e = 0; e < E; ++e) {
+    const int rows = tiles_per_expert[e] * tile_rows;
+    if (rows <= 0) continue;
+    const int rc = lia_gemm_bf16(a + at * K, w + (size_t)e * w_expert_stride, nullptr, nullptr, c + at * N, rows, N, K, LIA_EPI_BIAS, nullptr,
+                                 workspace, workspace_bytes, stream_);
+    if (rc != LIA_OK) return rc;
+    at += rows;
+  }
+  return LIA_OK;
+}
+
 extern "C" int lia_moe_combine(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int shared_f32, float* y,
                                int M, int W, int top, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);

@@ -576,6 +576,21 @@ def moe_gather(src, perm, dst, top):
     return dst
 
 
+def moe_expert_gemms(a, w, out, tiles_per_expert, tile_rows, workspace):
+    """out[rows of e] = a[rows of e] @ w[e].T on the tensor-core GEMM, expert after expert: expert e owns the next
+    ``tiles_per_expert[e] * tile_rows`` rows of ``a`` and ``out`` (bf16; ``tiles_per_expert`` is a host list)."""
+    _req(a, "a"); _req(w, "w"); _req(out, "out")
+    E, N, K = w.shape
+    rows = sum(tiles_per_expert) * tile_rows
+    if len(tiles_per_expert) != E or a.shape[1] != K or out.shape[1] != N or a.shape[0] < rows or out.shape[0] < rows:
+        raise _lib.LiaError(f"moe_expert_gemms: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, {rows} rows planned")
+    counts = (ctypes.c_int * E)(*tiles_per_expert)
+    check(_lib.load().lia_moe_expert_gemms(_p(a), _p(w), N * K, _p(out), counts, E, tile_rows, N, K, workspace.buf.data_ptr(), workspace.buf.numel(),
+                                           _stream()), "lia_moe_expert_gemms")
+    count_launches(sum(1 for n in tiles_per_expert if n))
+    return out
+
+
 def moe_combine(ypair, shared, y, top, pos_of=None, wt=None):
     """y[m] = sum over the token's choices (+ the shared expert's output).  Without a plan ``ypair`` holds the weighted
     outputs pair by pair; with ``pos_of`` and ``wt`` it holds the unweighted outputs in the plan's order."""

@@ -328,9 +328,10 @@ class MoEFeedForward:
         W = self.w_up.shape[2]
         self.tensor_core = dtype == BF16 and W % 8 == 0 and ff % 8 == 0 and os.environ.get("LIA_PLAIN_LINEAR", "0") == "0"
 
-    def _workspace(self, M, N, K, device):
-        key = (device, M <= 128)
-        need = ops.GemmWorkspace.bytes_for([(M, N, K)])
+    def _workspace(self, rows, N, K, device):
+        """One split-K workspace large enough for every row count among the experts' launches."""
+        key = (device, "experts")
+        need = ops.GemmWorkspace.bytes_for([(m, N, K) for m in set(rows)])
         ws = Linear._gemm_ws.get(key)
         if ws is None or ws.buf.numel() < need:
             ws = Linear._gemm_ws[key] = ops.GemmWorkspace(need, device)
@@ -338,7 +339,7 @@ class MoEFeedForward:
 
     def _experts_tensor_core(self, h, idx, wt, y):
         """Prompts: the pairs grouped by expert (tiles of 64 rows), the rows gathered into that order, then one tensor-core
-        GEMM per expert and projection on its contiguous rows.  The tile table comes to the host once per call (the only
+        GEMM per expert and projection on its contiguous rows (launched back to back from the library).  The tile table comes to the host once per call (the only
         round trip; decode steps never take this path, so they stay capturable)."""
         M, W = h.shape
         E, top, ff, dev = self.E, self.top, self.ff, h.device
@@ -351,21 +352,13 @@ class MoEFeedForward:
         xs = torch.empty(n_tiles * tm, W, dtype=self.dtype, device=dev)
         ops.moe_gather(h, perm, xs, top)
         counts = torch.bincount(tile_expert.cpu().long() + 1, minlength=E + 1)[1:].tolist()          # tiles per expert
-        used = sum(counts) * tm
+        used, rows = sum(counts) * tm, [n * tm for n in counts if n]
         up = torch.empty(used, ff, dtype=self.dtype, device=dev)
-        at = 0
-        for e, n in enumerate(counts):
-            if n:
-                ops.gemm(xs[at:at + n * tm], self.w_up[e], None, out=up[at:at + n * tm], workspace=self._workspace(n * tm, ff, W, dev))
-                at += n * tm
+        ops.moe_expert_gemms(xs, self.w_up, up, counts, tm, self._workspace(rows, ff, W, dev))
         mid = torch.empty(used, ff, dtype=self.dtype, device=dev)
         ops.gated_act(up, ff, mid, self.act)
         ys = torch.empty(used, W, dtype=self.dtype, device=dev)
-        at = 0
-        for e, n in enumerate(counts):
-            if n:
-                ops.gemm(mid[at:at + n * tm], self.w_down[e], None, out=ys[at:at + n * tm], workspace=self._workspace(n * tm, W, ff, dev))
-                at += n * tm
+        ops.moe_expert_gemms(mid, self.w_down, ys, counts, tm, self._workspace(rows, W, ff, dev))
         ops.moe_combine(ys, self.shared(h) if self.shared is not None else None, y, top, pos_of=pos_of, wt=wt)
         return y
 
