@@ -55,9 +55,14 @@ class BebulornConfig:
             if l.get("type") not in MIXERS:
                 raise ValueError(f"layer {i}: unknown mixer type {l.get('type')!r} (known: {MIXERS})")
             mlp = l.get("mlp")
-            if mlp is not None and mlp.get("kind") not in MLP_KINDS:
-                raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r} (known: {MLP_KINDS})")
+            if mlp is not None:
+                mlp.setdefault("kind", "moe" if "router" in mlp else "dense")
+                if mlp["kind"] not in MLP_KINDS:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {mlp['kind']!r} (known: {MLP_KINDS})")
             m = l["mixer"]
+            m.setdefault("vdim", m["dim"])                       # value heads as wide as query/key heads unless said otherwise
+            if l["type"] != "lightning":
+                m.setdefault("kv_heads", m["heads"])             # ungrouped unless said otherwise
             if l["type"] != "lightning" and m["heads"] % m["kv_heads"]:
                 raise ValueError(f"layer {i}: {m['heads']} heads do not divide into {m['kv_heads']} groups")
             if l["type"] == "lightning":

@@ -45,6 +45,17 @@ def test_config_rejects_unknown_parts():
         BebulornConfig.from_dict(config([lightning(1, 4, 4)], 10, 8, loop={"start": 1, "stop": 0, "times": 1}))
 
 
+def test_config_defaults_for_what_a_layer_leaves_out():
+    a = attention(4, 4, 8, 8, 5)
+    del a["mixer"]["kv_heads"], a["mixer"]["vdim"]
+    li = lightning(2, 8, 8, decay=[0.5, 0.5], mlp={"ff": 16})
+    li["mixer"]["decay"] = 0.5
+    c = BebulornConfig.from_dict(config([a, li], 10, 8))
+    s = c.tensor_shapes()
+    assert s["l0.mix.k"] == (32, 8) and s["l0.mix.v"] == (32, 8) and s["l1.mlp.gate"] == (16, 8)
+    assert c.layers[1]["mixer"]["decay"] == [0.5, 0.5] and c.layers[1]["mlp"]["kind"] == "dense"
+
+
 def test_registry_picks_the_class_from_config_json(tmp_path):
     d = tmp_path / "m"
     d.mkdir()
